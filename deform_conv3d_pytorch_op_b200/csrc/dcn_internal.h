@@ -1,0 +1,34 @@
+// Internal interfaces between the C-ABI layer (dcn_api.cu) and the kernel files of libdcn.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "dcn_common.cuh"
+
+namespace dcn {
+
+// EXACT-precision (SIMT) launchers, dcn_simt.cu.  dtype: 0 fp32, 1 fp64.  Return 0 or -5 (launch failure).
+int simt_forward(const Geom& g, int dtype, int ndim, int deform, const void* x, const void* off, const void* w,
+                 const void* bias, void* y, cudaStream_t st);
+int simt_backward_data(const Geom& g, int dtype, int ndim, int deform, const void* x, const void* off,
+                       const void* w, const void* dy, void* dx, void* doff, cudaStream_t st);
+int simt_backward_weight(const Geom& g, int dtype, int ndim, int deform, const void* x, const void* off,
+                         const void* dy, void* dw, cudaStream_t st);
+int bias_grad(const Geom& g, int dtype, const void* dy, void* dbias, cudaStream_t st);
+int debug_points(const Geom& g, int dtype, int ndim, const void* off, int n, void* coords, int32_t* valid,
+                 int32_t* lo, int32_t* hi, cudaStream_t st);
+
+// BF16 tensor-core (tcgen05) path, dcn_tc.cu.  fp32 tensors only.
+bool tc_supported(const Geom& g, int ndim, int deform);
+size_t tc_workspace_bytes(const Geom& g, int ndim, int pass);
+int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+               const float* bias, float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+                     const float* dy, float* dx, float* doff, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* dy,
+                       float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_check_status(cudaStream_t st);
+
+}  // namespace dcn

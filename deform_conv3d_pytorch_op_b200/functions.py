@@ -1,0 +1,118 @@
+"""autograd Functions with the reference's call signatures.
+
+* :class:`ConvOffset3dFunction` -- deform3d/deform_conv3d_functions/deform_conv3d_function.py:7-77
+* :class:`ConvOffset2dFunction` -- deform2d_double/deform_conv2d_functions/deform_conv2d_function.py:7-77
+* :class:`Conv2dFunction`       -- conv2d/conv2d_functions/conv2d_function.py:8-67
+* :class:`LegacyConvOffset2dFunction` -- the stateful fp32 2-D form,
+  deform2d/deform_conv2d_functions/deform_conv2d_function.py:7-57
+
+``.apply`` keeps the reference's positional order; ``backward`` returns the same slots.  Differences:
+gradients are computed only for the inputs that need them (the reference always computes dX and dOffset
+together), and two optional trailing arguments select the arithmetic (``precision``: exact | bf16 | auto)
+and the 3-D out-of-bounds offset pseudo-gradient (``oob_offset_grad``).
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+from torch.autograd.function import once_differentiable
+
+from .ops import Op
+
+
+def _tup(v, n):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v,) * n
+
+
+class _ConvOffsetNdFunction(Function):
+    NDIM = 0
+
+    @staticmethod
+    def _fwd(ndim, ctx, inputs, offset, weight, bias, stride, padding, dilation, channel_per_group, group,
+             precision, oob_offset_grad):
+        if inputs.dim() != ndim + 2:
+            raise RuntimeError("input dim")
+        ctx.op = Op(inputs, weight, _tup(stride, ndim), _tup(padding, ndim), _tup(dilation, ndim), channel_per_group,
+                    group, deformable=True, std_size_rule=False, oob_offset_grad=oob_offset_grad,
+                    precision=precision)
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(inputs, offset, weight)
+        return ctx.op.forward(inputs, offset, weight, bias)
+
+    @staticmethod
+    def _bwd(ctx, grad_output):
+        inputs, offset, weight = ctx.saved_tensors
+        need = ctx.needs_input_grad
+        grad_input = grad_offset = grad_weight = grad_bias = None
+        if need[0] or need[1]:
+            grad_input, grad_offset = ctx.op.backward_data(inputs, offset, weight, grad_output, need[0], need[1])
+        want_db = ctx.has_bias and need[3]
+        if need[2] or want_db:
+            grad_weight, grad_bias = ctx.op.backward_weight(inputs, offset, grad_output, need[2], want_db)
+        return grad_input, grad_offset, grad_weight, grad_bias
+
+
+class ConvOffset3dFunction(_ConvOffsetNdFunction):
+    @staticmethod
+    def forward(ctx, inputs, offset, weight, bias=None, stride=(1, 1, 1), padding=(0, 0, 0), dilation=(1, 1, 1),
+                channel_per_group=1, group=1, precision=None, oob_offset_grad=None):
+        return _ConvOffsetNdFunction._fwd(3, ctx, inputs, offset, weight, bias, stride, padding, dilation,
+                                          channel_per_group, group, precision, oob_offset_grad)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        return _ConvOffsetNdFunction._bwd(ctx, grad_output) + (None,) * 7
+
+
+class ConvOffset2dFunction(_ConvOffsetNdFunction):
+    @staticmethod
+    def forward(ctx, inputs, offset, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1),
+                channel_per_group=1, group=1, precision=None, oob_offset_grad=None):
+        return _ConvOffsetNdFunction._fwd(2, ctx, inputs, offset, weight, bias, stride, padding, dilation,
+                                          channel_per_group, group, precision, oob_offset_grad)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        return _ConvOffsetNdFunction._bwd(ctx, grad_output) + (None,) * 7
+
+
+class Conv2dFunction(Function):
+    @staticmethod
+    def forward(ctx, inputs, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), group=1,
+                precision=None):
+        if inputs.dim() != 4:
+            raise RuntimeError("input dim")
+        ctx.op = Op(inputs, weight, _tup(stride, 2), _tup(padding, 2), _tup(dilation, 2), inputs.size(1), group,
+                    deformable=False, std_size_rule=True, precision=precision)
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(inputs, weight)
+        return ctx.op.forward(inputs, None, weight, bias)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad_output):
+        inputs, weight = ctx.saved_tensors
+        need = ctx.needs_input_grad
+        grad_input = grad_weight = grad_bias = None
+        if need[0]:
+            grad_input, _ = ctx.op.backward_data(None, None, weight, grad_output, True, False)
+        want_db = ctx.has_bias and need[2]
+        if need[1] or want_db:
+            grad_weight, grad_bias = ctx.op.backward_weight(inputs, None, grad_output, need[1], want_db)
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None
+
+
+class LegacyConvOffset2dFunction:
+    """``ConvOffset2dFunction(stride, padding, channel_per_group)(input, offset, weight)`` -- the stateful call
+    form of the fp32 2-D package (no dilation, no groups, no bias)."""
+
+    def __init__(self, stride, padding, channel_per_group):
+        self.stride = _tup(stride, 2)
+        self.padding = _tup(padding, 2)
+        self.channel_per_group = channel_per_group
+
+    def __call__(self, inputs, offset, weight):
+        return ConvOffset2dFunction.apply(inputs, offset, weight, None, self.stride, self.padding, (1, 1),
+                                          self.channel_per_group, 1)

@@ -1,0 +1,176 @@
+"""Tensor-level entry points over the C ABI: the three passes of the operator on torch CUDA tensors.
+
+These are the counterparts of the reference's FFI calls (``deform_conv3d_op.deform_conv_forward_cuda`` and
+siblings, deform3d/lib/deform_conv3d_cuda.h:12-34) with the output allocation the reference does in Python
+(deform3d/deform_conv3d_functions/deform_conv3d_function.py:26-32, 53-54, 64) folded in.  torch is used for
+device memory and the current stream only; all arithmetic happens in libdcn.so.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import DcnError
+
+_PRECISIONS = {"exact": _lib.PREC_EXACT, "fp32": _lib.PREC_EXACT, "bf16": _lib.PREC_BF16}
+
+
+def default_precision() -> str:
+    """``DCN_PRECISION`` = exact | bf16 | auto (default exact: compute in the tensor dtype)."""
+    return os.environ.get("DCN_PRECISION", "exact").lower()
+
+
+def default_oob_offset_grad() -> bool:
+    """``DCN_OOB_OFFSET_GRAD`` = reference | zero (default reference; only 3-D has the term)."""
+    return os.environ.get("DCN_OOB_OFFSET_GRAD", "reference").lower() != "zero"
+
+
+def _prep(t: Optional[torch.Tensor], name: str, ref: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise DcnError("%s must be a CUDA tensor (there is no CPU implementation)" % name)
+    if ref is not None:
+        if t.device != ref.device:
+            raise DcnError("%s is on %s but input is on %s" % (name, t.device, ref.device))
+        if t.dtype != ref.dtype:
+            raise DcnError("%s has dtype %s but input has %s" % (name, t.dtype, ref.dtype))
+    return t.contiguous()
+
+
+class Op:
+    """One validated operator instance (geometry + precision) bound to a device."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, channel_per_group: int,
+                 group: int, deformable: bool = True, std_size_rule: bool = False,
+                 oob_offset_grad: Optional[bool] = None, precision: Optional[str] = None):
+        ndim = x.dim() - 2
+        if ndim not in (2, 3):
+            raise DcnError("input dim")                       # reference: check(input_dim == 5, "input dim")
+        if weight.dim() != ndim + 2:
+            raise DcnError("kernel dim")
+        if x.size(1) != weight.size(1) * group:
+            raise DcnError("input c != kernel c")
+        self.ndim = ndim
+        self.device = x.device
+        self.dtype = x.dtype
+        prec = (precision or default_precision()).lower()
+        if oob_offset_grad is None:
+            oob_offset_grad = default_oob_offset_grad()
+        cpg = channel_per_group if deformable else x.size(1)
+        mk = lambda pr: _lib.make_problem(ndim, x.dtype, x.size(0), x.size(1), weight.size(0), tuple(x.shape[2:]),
+                                          tuple(weight.shape[2:]), stride, padding, dilation, group, cpg,
+                                          deformable, std_size_rule, oob_offset_grad, pr)
+        if prec == "auto":
+            p = mk(_lib.PREC_BF16) if x.dtype == torch.float32 else None
+            if p is None or not _lib.lib().dcn_precision_supported(ctypes.byref(p)):
+                p = mk(_lib.PREC_EXACT)
+        elif prec in _PRECISIONS:
+            p = mk(_PRECISIONS[prec])
+        else:
+            raise DcnError("unknown precision %r (exact | bf16 | auto)" % prec)
+        _lib.check(_lib.lib().dcn_validate(ctypes.byref(p)), "shape check")
+        if not _lib.lib().dcn_precision_supported(ctypes.byref(p)):
+            raise DcnError("precision %r is not available for this problem (needs float32 tensors and channel "
+                           "counts per group that are multiples of 8); there is no silent fallback" % prec)
+        self.p = p
+        self.deformable = deformable
+        self.out_size = _lib.output_size(p)
+        self.offset_channels = (x.size(1) // cpg) * int(torch.Size(weight.shape[2:]).numel()) * ndim
+        self.N, self.C, self.O = x.size(0), x.size(1), weight.size(0)
+        self.weight_shape = tuple(weight.shape)
+
+    # -- helpers ---------------------------------------------------------------------------------
+    def _ws(self, which: int):
+        nbytes = _lib.lib().dcn_workspace_bytes(ctypes.byref(self.p), which)
+        if nbytes == 0:
+            return None, 0
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return ws, nbytes
+
+    def _check_offset(self, offset: torch.Tensor):
+        want = (self.N, self.offset_channels) + tuple(self.out_size)
+        if tuple(offset.shape) != want:
+            raise DcnError("offset shape %s, expected %s" % (tuple(offset.shape), want))
+
+    # -- passes ----------------------------------------------------------------------------------
+    def forward(self, x, offset, weight, bias=None) -> torch.Tensor:
+        x = _prep(x, "input")
+        weight = _prep(weight, "weight", x)
+        bias = _prep(bias, "bias", x)
+        if self.deformable:
+            offset = _prep(offset, "offset", x)
+            self._check_offset(offset)
+        else:
+            offset = None
+        y = torch.empty((self.N, self.O) + tuple(self.out_size), dtype=x.dtype, device=x.device)
+        ws, nb = self._ws(_lib.PASS_FORWARD)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dcn_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
+                                        _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), nb, _lib.current_stream(x.device))
+        _lib.check(st, "dcn_forward")
+        return y
+
+    def backward_data(self, x, offset, weight, dy, want_dx=True, want_doffset=True
+                      ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        weight = _prep(weight, "weight")
+        dy = _prep(dy, "grad_output", weight)
+        dx = doff = None
+        if self.deformable:
+            x = _prep(x, "input", weight)
+            offset = _prep(offset, "offset", weight)
+            self._check_offset(offset)
+        else:
+            offset = None
+            want_doffset = False
+        if want_dx:
+            dx = torch.zeros((self.N, self.C) + tuple(self.p.in_)[3 - self.ndim:], dtype=dy.dtype, device=dy.device)
+        if want_doffset:
+            doff = torch.empty((self.N, self.offset_channels) + tuple(self.out_size), dtype=dy.dtype, device=dy.device)
+        if dx is None and doff is None:
+            return None, None
+        ws, nb = self._ws(_lib.PASS_BACKWARD_DATA)
+        with torch.cuda.device(dy.device):
+            st = _lib.lib().dcn_backward_data(ctypes.byref(self.p), _lib.ptr(x) if self.deformable else None,
+                                              _lib.ptr(offset), _lib.ptr(weight), _lib.ptr(dy), _lib.ptr(dx),
+                                              _lib.ptr(doff), _lib.ptr(ws), nb, _lib.current_stream(dy.device))
+        _lib.check(st, "dcn_backward_data")
+        return dx, doff
+
+    def backward_weight(self, x, offset, dy, want_dw=True, want_dbias=False
+                        ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        x = _prep(x, "input")
+        dy = _prep(dy, "grad_output", x)
+        offset = _prep(offset, "offset", x) if self.deformable else None
+        dw = torch.zeros(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
+        db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
+        if dw is None and db is None:
+            return None, None
+        ws, nb = self._ws(_lib.PASS_BACKWARD_WEIGHT) if want_dw else (None, 0)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dcn_backward_weight(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(dy),
+                                                _lib.ptr(dw), _lib.ptr(db), _lib.ptr(ws), nb,
+                                                _lib.current_stream(x.device))
+        _lib.check(st, "dcn_backward_weight")
+        return dw, db
+
+    def debug_points(self, offset: torch.Tensor, n: int):
+        """Coordinates / validity / corner indices of sample ``n`` as the device routine computes them."""
+        offset = _prep(offset, "offset")
+        dg, kv, ov = self.C // self.p.cpg, self.offset_channels // (self.C // self.p.cpg) // self.ndim, 1
+        for s in self.out_size:
+            ov *= s
+        coords = torch.empty((dg, kv, ov, self.ndim), dtype=offset.dtype, device=offset.device)
+        valid = torch.empty((dg, kv, ov), dtype=torch.int32, device=offset.device)
+        lo = torch.empty((dg, kv, ov, self.ndim), dtype=torch.int32, device=offset.device)
+        hi = torch.empty_like(lo)
+        with torch.cuda.device(offset.device):
+            st = _lib.lib().dcn_debug_points(ctypes.byref(self.p), _lib.ptr(offset), n, _lib.ptr(coords),
+                                             _lib.ptr(valid), _lib.ptr(lo), _lib.ptr(hi),
+                                             _lib.current_stream(offset.device))
+        _lib.check(st, "dcn_debug_points")
+        return coords, valid, lo, hi

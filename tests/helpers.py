@@ -1,0 +1,68 @@
+"""Shared helpers of the GPU parity tests."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import oracle as orc
+from tests import cases
+
+
+def run_ours(case, tensors, precision="exact", oob=True, device="cuda"):
+    """fwd + bwd through the public Functions (autograd) on the CUDA path; numpy results."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    x, w, off, dy, b = [None if t is None else t.to(device) for t in tensors]
+    x = x.clone().requires_grad_(True)
+    w = w.clone().requires_grad_(True)
+    if b is not None:
+        b = b.clone().requires_grad_(True)
+    if case.deformable:
+        off = off.clone().requires_grad_(True)
+        fn = dcn.ConvOffset3dFunction if case.ndim == 3 else dcn.ConvOffset2dFunction
+        y = fn.apply(x, off, w, b, case.stride, case.pad, case.dil, case.cpg, case.G, precision, oob)
+    else:
+        y = dcn.Conv2dFunction.apply(x, w, b, case.stride, case.pad, case.dil, case.G, precision)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    out = {"y": y.detach().cpu().numpy(), "dx": x.grad.cpu().numpy(), "dw": w.grad.cpu().numpy()}
+    if case.deformable:
+        out["doff"] = off.grad.cpu().numpy()
+    if b is not None:
+        out["db"] = b.grad.cpu().numpy()
+    return out
+
+
+def run_oracle(case, tensors, dtype=None, oob=True):
+    """Same pass on the CPU oracle, optionally in another dtype (float64 = the tolerance oracle)."""
+    x, w, off, dy, b = [None if t is None else t.numpy() for t in tensors]
+    if dtype is not None:
+        x, w, dy = x.astype(dtype), w.astype(dtype), dy.astype(dtype)
+        off = None if off is None else off.astype(dtype)
+        b = None if b is None else b.astype(dtype)
+    p = case.problem(oob=oob)
+    p.N = x.shape[0]
+    out = {"y": orc.forward(p, x, off, w, b)}
+    out["dx"], doff = orc.backward_data(p, x, off, w, dy)
+    if doff is not None:
+        out["doff"] = doff
+    out["dw"] = orc.backward_weight(p, x, off, dy)
+    if b is not None:
+        out["db"] = orc.backward_bias(p, dy)
+    return out
+
+
+def lattice_mask(case, off_np, tol=1e-5):
+    """True where some coordinate of the sampling point lies within tol of the integer lattice (there the
+    offset derivative is one-sided and fp32 / fp64 coordinates may pick different sides).  Shape of doff."""
+    p = case.problem()
+    N = off_np.shape[0]
+    p.N = N
+    mask = np.zeros(off_np.shape, dtype=bool)
+    nd = case.ndim
+    for n in range(N):
+        pts, valid, lo, hi = orc.dump_points(p, np.ascontiguousarray(off_np[n].astype(np.float32)))
+        frac = np.abs(pts - np.round(pts))
+        near = (frac < tol).any(axis=-1)            # [dg, kv, ov]
+        near = np.repeat(near[:, :, None, :], nd, axis=2).reshape((-1,) + tuple(p.out_size))
+        mask[n] = near
+    return mask

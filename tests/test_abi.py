@@ -1,0 +1,93 @@
+"""CPU checks of the C-ABI library: it loads, exports every symbol include/dcn.h declares, and its host-side
+argument contract (the reference's shape_check) answers without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from deform_conv3d_pytorch_op_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    build.build()
+    return _lib.lib()
+
+
+def test_header_symbols_are_exported(L):
+    text = open(os.path.join(ROOT, "include", "dcn.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = set(re.findall(r"\b(dcn_[a-z0-9_]+)\s*\(", text))
+    assert len(declared) >= 20
+    assert declared == set(_lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS + [s for s in declared if s not in
+                                                                        _lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS])
+    for sym in sorted(declared):
+        assert hasattr(L, sym), sym
+    for sym in _lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS:
+        assert sym in declared, sym
+
+
+def _p(**kw):
+    base = dict(ndim=2, dtype=torch.float32, N=2, C=4, O=6, in_size=(7, 7), kernel=(3, 3), stride=(1, 1), pad=(1, 1),
+                dil=(1, 1), G=2, cpg=2)
+    base.update(kw)
+    return _lib.make_problem(**base)
+
+
+def test_output_size_rules(L):
+    # deformable rule ignores dilation (deform3d/lib/deform_conv3d_cuda.cpp:15-17)
+    assert _lib.output_size(_p(dil=(2, 2), pad=(2, 2), stride=(2, 2))) == (5, 5)
+    # plain conv rule is dilation-aware (conv2d/lib/conv2d_cuda.cpp:20-22)
+    assert _lib.output_size(_p(dil=(2, 2), pad=(2, 2), stride=(2, 2), deformable=False, std_size_rule=True)) == (4, 4)
+    # BASELINE config 4: 8x28x28, k3, stride (1,2,2), pad 2, dilation 2 -> 10x15x15
+    p = _lib.make_problem(3, torch.float32, 16, 128, 256, (8, 28, 28), (3, 3, 3), (1, 2, 2), (2, 2, 2), (2, 2, 2), 4, 16)
+    assert _lib.output_size(p) == (10, 15, 15)
+
+
+def test_shape_contract(L):
+    ok = _p()
+    assert L.dcn_validate(ctypes.byref(ok)) == 0
+    assert L.dcn_validate(ctypes.byref(_p(C=5))) == -2           # C % G
+    assert L.dcn_validate(ctypes.byref(_p(O=5))) == -2           # O % G
+    assert L.dcn_validate(ctypes.byref(_p(cpg=3))) == -2         # C % cpg
+    assert L.dcn_validate(ctypes.byref(_p(in_size=(1, 1), pad=(0, 0)))) == -2   # empty output
+    bad = _p()
+    bad.ndim = 4
+    assert L.dcn_validate(ctypes.byref(bad)) == -3
+    assert L.dcn_validate(ctypes.byref(_p(precision=_lib.PREC_BF16, dtype=torch.float64))) == -3
+    assert L.dcn_status_string(-2).decode().startswith("sizes")
+    assert L.dcn_workspace_bytes(ctypes.byref(ok), 0) == 0       # EXACT precision needs no scratch
+
+
+def test_null_pointers_are_refused_before_any_launch(L):
+    ok = _p()
+    assert L.dcn_forward(ctypes.byref(ok), None, None, None, None, None, None, 0, None) == -1
+    assert L.dcn_backward_data(ctypes.byref(ok), None, None, None, None, None, None, None, 0, None) == -1
+    assert L.dcn_backward_weight(ctypes.byref(ok), None, None, None, None, None, None, 0, None) == -1
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdcn.so")
+    with pytest.raises(_lib.DcnError):
+        _lib.lib()
+
+
+def test_module_surface():
+    import deform_conv3d_pytorch_op_b200 as dcn
+    m = dcn.ConvOffset3d(8, 16, 3, stride=1, padding=1, dilation=1, channel_per_group=2, bias=True, groups=2)
+    assert tuple(m.weight.shape) == (16, 4, 3, 3, 3) and tuple(m.bias.shape) == (16,)
+    assert m.offset_channels == 4 * 27 * 3
+    assert set(m.state_dict().keys()) == {"weight", "bias"}
+    m2 = dcn.DeformConv2d(8, 8, 3, deformable_groups=4, bias=False)
+    assert m2.channel_per_group == 2 and m2.bias is None and m2.offset_channels == 4 * 9 * 2
+    with pytest.raises(ValueError):
+        dcn.ConvOffset3d(6, 8, 3, groups=4)
+    leg = dcn.LegacyConvOffset2d(4, 4, 3, 1, 1, 2)
+    assert leg.bias is None and leg.dilation == (1, 1)
+    c = dcn.Conv2d(4, 6, 3, groups=2)
+    assert tuple(c.weight.shape) == (6, 2, 3, 3)
