@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the one hot path: deformable convolution forward + backward (dX, dOffset, dW).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1|2|3|4] [--precision auto|exact|bf16]
+    python bench.py --impl reference ...      # the reference algorithm on the host cores (CPU oracle port)
+
+One "step" is one forward + backward-data + backward-weight pass of the configured workload over a batch of
+seeded synthetic tensors.  Prints ONE JSON line (rank 0).  Under torchrun every rank runs the same per-GPU
+batch (weak scaling) and the weight gradient -- the only quantity that sums over the batch -- is all-reduced
+with NCCL inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "deform_conv_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region (read-only)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [a.strip() for a in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_port_run(wl, n_samples: int, repeats: int = 1):
+    """Times the CPU oracle (the reference algorithm restated) on `n_samples` samples of the workload."""
+    import numpy as np
+    from oracle import oracle as orc
+    from deform_conv3d_pytorch_op_b200 import workloads
+    x, w, off, dy = [t.numpy() for t in workloads.make_inputs(wl, n=n_samples)]
+    p = orc.Problem(wl.ndim, n_samples, wl.C, wl.O, wl.in_size, wl.kernel, wl.stride, wl.pad, wl.dil, wl.G, wl.cpg)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.fwd_bwd(p, x, off, w, dy)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_reference(args, wl):
+    """--impl reference: the reference algorithm on the host cores.  The reference ships CUDA kernels only
+    and no CPU path, so this is the oracle port (kind "port"), with all host threads (OpenMP + BLAS)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    n = max(1, min(wl.N, args.ref_samples))
+    from oracle import oracle as orc
+    orc.build()
+    for _ in range(args.warmup):
+        cpu_port_run(wl, n)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_port_run(wl, n)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = wl.flops(n) / dt / 1e12
+    sample = "%d of %d samples per step, forward + backward (dX, dOffset, dW), fp32" % (n, wl.N)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.name, "samples_per_step": n},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4])
+    ap.add_argument("--precision", default="auto", choices=["auto", "exact", "bf16"])
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (0: the configuration's)")
+    ap.add_argument("--ref-samples", type=int, default=8, help="samples per step of the --impl reference arm")
+    ap.add_argument("--cpu-baseline-samples", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    from deform_conv3d_pytorch_op_b200 import workloads
+    wl = workloads.CONFIGS[args.config]
+    if args.batch > 0:
+        import dataclasses
+        wl = dataclasses.replace(wl, N=args.batch)
+
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    import deform_conv3d_pytorch_op_b200 as dcn
+    from deform_conv3d_pytorch_op_b200 import _lib
+    import ctypes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU implementation)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    # every rank draws its own batch (seed = rank): weak scaling, no data-path collective but the dW all-reduce
+    x_h, w_h, off_h, dy_h = workloads.make_inputs(wl, seed=rank, pin=True)
+    w_h0 = workloads.make_inputs(wl, seed=0, n=1)[1]
+    w_h.copy_(w_h0)                                   # the weight is replicated
+    x, w, off, dy = [t.to(dev) for t in (x_h, w_h, off_h, dy_h)]
+
+    op = dcn.Op(x, w, wl.stride, wl.pad, wl.dil, wl.cpg, wl.G, precision=args.precision)
+    prec = "bf16" if op.p.precision == _lib.PREC_BF16 else "exact"
+    launches_per_step = sum(_lib.lib().dcn_launch_count(ctypes.byref(op.p), ps) for ps in (0, 1, 2))
+
+    # L2 hygiene: the working set of configs 2-4 is several times the 126 MB L2; for small ones flush.
+    working_set = sum(t.numel() * 4 for t in (x, off, dy)) * 2 + x.numel() * 4
+    flush = working_set < 512 * 1024 * 1024
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush else None
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    pass_ms = {"forward": 0.0, "backward_data": 0.0, "backward_weight": 0.0}
+
+    def step(timed: bool):
+        if flush:
+            flush_buf.zero_()
+        e = [ev() for _ in range(4)] if timed else None
+        if timed:
+            e[0].record()
+        y = op.forward(x, off, w, None)
+        if timed:
+            e[1].record()
+        dx, doff = op.backward_data(x, off, w, dy)
+        if timed:
+            e[2].record()
+        dw, _ = op.backward_weight(x, off, dy)
+        if timed:
+            e[3].record()
+        if world > 1:
+            dist.all_reduce(dw)
+        return e, (y, dx, doff, dw)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step(False)
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_begin, t_end = ev(), ev()
+    evs = []
+    flush_ms = 0.0
+    sync_all()
+    t_begin.record()
+    for _ in range(args.steps):
+        e, _ = step(True)
+        evs.append(e)
+    t_end.record()
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_begin.elapsed_time(t_end)
+    for e in evs:
+        pass_ms["forward"] += e[0].elapsed_time(e[1])
+        pass_ms["backward_data"] += e[1].elapsed_time(e[2])
+        pass_ms["backward_weight"] += e[2].elapsed_time(e[3])
+    for k in pass_ms:
+        pass_ms[k] /= args.steps
+    if flush:
+        # the flush memset sits inside the bracket; measure it alone and take it out
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(args.steps):
+            flush_buf.zero_()
+        b.record()
+        torch.cuda.synchronize()
+        flush_ms = a.elapsed_time(b)
+    ms_per_step = (total_ms - flush_ms) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_per_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_per_step = float(t.item())
+    st = _lib.lib().dcn_check_status(_lib.current_stream(dev))
+    _lib.check(st, "device status after the timed region")
+    value = wl.flops() * world / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host tensors in, results back to the host, through the public autograd API ----
+    e2e = None
+    if not args.no_e2e:
+        fn = dcn.ConvOffset3dFunction if wl.ndim == 3 else dcn.ConvOffset2dFunction
+        outs_h = None
+
+        def e2e_step():
+            nonlocal outs_h
+            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+            od = off_h.to(dev, non_blocking=True).requires_grad_(True)
+            wd = w_h.to(dev, non_blocking=True).requires_grad_(True)
+            dyd = dy_h.to(dev, non_blocking=True)
+            yd = fn.apply(xd, od, wd, None, wl.stride, wl.pad, wl.dil, wl.cpg, wl.G, prec)
+            yd.backward(dyd)
+            if world > 1:
+                dist.all_reduce(wd.grad)
+            res = (yd.detach(), xd.grad, od.grad, wd.grad)
+            if outs_h is None:
+                outs_h = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in res]
+            for h, t in zip(outs_h, res):
+                h.copy_(t, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 10))
+        for _ in range(2):
+            e2e_step()
+        sync_all()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        sync_all()
+        e2e_ms = a.elapsed_time(b) / n_e2e
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        h2d = sum(t.numel() * t.element_size() for t in (x_h, off_h, w_h, dy_h))
+        d2h = sum(t.numel() * t.element_size() for t in outs_h)
+        e2e = {"value": wl.flops() * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    if rank == 0:
+        peaks = _peaks()
+        dom = max(pass_ms, key=pass_ms.get)
+        per_pass_flops = wl.flops() / 3.0
+        fwd_b, bwd_b = wl.bytes_alg()
+        t_tc = per_pass_flops / (peaks["bf16_tflops"] * 1e12)
+        pass_bytes = wl.bytes_per_pass()[dom]
+        t_hbm = pass_bytes / (peaks["hbm_gbs"] * 1e9)
+        if t_tc >= t_hbm:
+            ach = per_pass_flops / (pass_ms[dom] * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": ach / peaks["bf16_tflops"]}
+        else:
+            ach = pass_bytes / (pass_ms[dom] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": ach / peaks["hbm_gbs"]}
+        roof.update({"kernel": dom, "kernel_ms": pass_ms[dom], "traffic": None, "peak_source": peaks["source"],
+                     "pass_ms": pass_ms,
+                     "whole_step_frac": max(wl.flops() / (peaks["bf16_tflops"] * 1e12),
+                                            (fwd_b + bwd_b) / (peaks["hbm_gbs"] * 1e9)) / (ms_per_step * 1e-3)})
+        cpu = None
+        if not args.no_cpu_baseline:
+            from oracle import oracle as orc
+            orc.build()
+            n = max(1, min(wl.N, args.cpu_baseline_samples))
+            cpu_port_run(wl, 1)
+            dt = cpu_port_run(wl, n)
+            cpu = {"value": wl.flops(n) / dt / 1e12, "unit": UNIT, "cores": len(os.sched_getaffinity(0)),
+                   "kind": "port", "seconds": dt,
+                   "sample": "%d of %d samples, forward + backward (dX, dOffset, dW), fp32 oracle port" % (n, wl.N)}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": wl.name, "per_gpu_batch": wl.N, "precision": prec, "io_dtype": "f32",
+                       "l2": "flushed between steps" if flush else "working set %.0f MB > 126 MB L2" %
+                             (working_set / 1e6),
+                       "parallelism": "batch-sharded x%d, dW all-reduce" % world if world > 1 else "single GPU"},
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -39,7 +39,7 @@ _lib: Optional[ctypes.CDLL] = None
 # every symbol include/dcn.h declares (checked by the CPU test-suite)
 GENERIC_SYMBOLS = [
     "dcn_version", "dcn_status_string", "dcn_output_size", "dcn_validate", "dcn_precision_supported",
-    "dcn_workspace_bytes", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_debug_points",
+    "dcn_workspace_bytes", "dcn_launch_count", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_debug_points",
     "dcn_check_status",
 ]
 LEGACY_SYMBOLS = [
@@ -71,6 +71,7 @@ def lib() -> ctypes.CDLL:
         L.dcn_precision_supported.argtypes = [pp]
         L.dcn_workspace_bytes.restype = ctypes.c_size_t
         L.dcn_workspace_bytes.argtypes = [pp, ctypes.c_int]
+        L.dcn_launch_count.argtypes = [pp, ctypes.c_int]
         L.dcn_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_backward_data.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_backward_weight.argtypes = [pp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]

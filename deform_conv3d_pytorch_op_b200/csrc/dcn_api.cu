@@ -119,6 +119,14 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
     return dcn::tc_workspace_bytes(g, p->ndim, pass);
 }
 
+int dcn_launch_count(const dcn_problem* p, int pass) {
+    if (validate(p) != DCN_OK) return 0;
+    if (p->precision == DCN_PREC_EXACT) return 1;
+    Geom g;
+    make_geom(p, g);
+    return dcn::tc_launch_count(g, p->ndim, pass);
+}
+
 int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* bias,
                 void* y, void* ws, size_t ws_bytes, void* stream) {
     const int v = validate(p);

@@ -30,5 +30,6 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
 int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* dy,
                        float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_check_status(cudaStream_t st);
+int tc_launch_count(const Geom& g, int ndim, int pass);
 
 }  // namespace dcn

@@ -93,6 +93,10 @@ int dcn_precision_supported(const dcn_problem* p);
 /* Scratch bytes `pass` needs (0 for the EXACT precision).  The workspace must be 256-byte aligned. */
 size_t dcn_workspace_bytes(const dcn_problem* p, int pass);
 
+/* Number of kernel launches `pass` enqueues for this problem (memsets not counted); used by callers
+ * that account for launches.  0 on an invalid problem. */
+int dcn_launch_count(const dcn_problem* p, int pass);
+
 /* y = conv(x sampled at offset, weight) + bias.  `offset` may be NULL when deformable == 0, `bias` may
  * be NULL.  y is overwritten.  Replaces deform_conv_forward_cuda (deform3d/lib/deform_conv3d_cuda.cpp:90-165)
  * and the Python-side bias add (deform3d/deform_conv3d_functions/deform_conv3d_function.py:41-42). */
