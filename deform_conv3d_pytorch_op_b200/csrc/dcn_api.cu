@@ -64,6 +64,11 @@ void make_geom(const dcn_problem* p, Geom& g) {
 
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+bool workspace_ok(const void* ws, size_t have, size_t need) {
+    if (need == 0) return true;
+    return ws != nullptr && have >= need && aligned(ws, 256);
+}
+
 int check_ptrs(const dcn_problem* p, std::initializer_list<const void*> ptrs) {
     const size_t es = p->dtype == DCN_F64 ? 8 : 4;
     for (const void* q : ptrs)
@@ -139,8 +144,7 @@ int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->precision == DCN_PREC_BF16) {
         if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
-        if (ws == nullptr || ws_bytes < dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_FORWARD) || !aligned(ws, 256))
-            return DCN_ERR_WORKSPACE;
+        if (!workspace_ok(ws, ws_bytes, dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_FORWARD))) return DCN_ERR_WORKSPACE;
         return dcn::tc_forward(g, p->ndim, p->deformable, (const float*)x, (const float*)offset,
                                (const float*)weight, (const float*)bias, (float*)y, ws, ws_bytes, st);
     }
@@ -161,7 +165,7 @@ int dcn_backward_data(const dcn_problem* p, const void* x, const void* offset, c
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (p->precision == DCN_PREC_BF16) {
         if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
-        if (ws == nullptr || ws_bytes < dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_BACKWARD_DATA) || !aligned(ws, 256))
+        if (!workspace_ok(ws, ws_bytes, dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_BACKWARD_DATA)))
             return DCN_ERR_WORKSPACE;
         return dcn::tc_backward_data(g, p->ndim, p->deformable, (const float*)x, (const float*)offset,
                                      (const float*)weight, (const float*)dy, (float*)dx, (float*)doffset, ws,
@@ -186,8 +190,7 @@ int dcn_backward_weight(const dcn_problem* p, const void* x, const void* offset,
     if (dweight != nullptr) {
         if (p->precision == DCN_PREC_BF16) {
             if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
-            if (ws == nullptr || ws_bytes < dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_BACKWARD_WEIGHT) ||
-                !aligned(ws, 256))
+            if (!workspace_ok(ws, ws_bytes, dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_BACKWARD_WEIGHT)))
                 return DCN_ERR_WORKSPACE;
             r = dcn::tc_backward_weight(g, p->ndim, p->deformable, (const float*)x, (const float*)offset,
                                         (const float*)dy, (float*)dweight, ws, ws_bytes, st);

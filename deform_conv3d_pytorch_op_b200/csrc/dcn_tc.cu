@@ -1,11 +1,463 @@
-// placeholder while the tensor-core path is being written
+// BF16 tensor-core path of libdcn (sm_100a): implicit-GEMM kernels on tcgen05 with accumulators in tensor
+// memory.  fp32 tensors in and out; sampled patches, weights and output gradients are rounded to bf16 on
+// their way into shared memory; coordinates, interpolation weights and accumulation stay fp32.
+//
+// Replaces, without ever materialising the reference's column buffer:
+//   forward          deformable_im2col + SGEMM       (deform3d/lib/deform_conv3d_cuda.cpp:105-149)
+//   backward data    SGEMM + col2im_offset + col2im  (deform3d/lib/deform_conv3d_cuda.cpp:186-251)
+//   backward weight  deformable_im2col + SGEMM(b=1)  (deform3d/lib/deform_conv3d_cuda.cpp:278-321)
+//
+// Internal layouts (workspace):
+//   x_cl   [N][in volume][C] bf16      channels-last copy of the input: the C/dg channels that share one
+//                                      sampling point are contiguous, so one corner fetch is a 16-byte load
+//   w_pk   pre-swizzled 128x64 bf16 operand tiles of the weight, GEMM-K ordered (tap, channel)
+//   dx_cl  [N][in volume][C] fp32      channels-last input-gradient accumulator (backward data)
+//
+// Requirements (dcn_precision_supported): fp32 tensors, C/G and C/dg multiples of 8.
 #include "dcn_internal.h"
+#include "dcn_tc_common.cuh"
+
 namespace dcn {
-bool tc_supported(const Geom&, int, int) { return false; }
-size_t tc_workspace_bytes(const Geom&, int, int) { return 0; }
-int tc_forward(const Geom&, int, int, const float*, const float*, const float*, const float*, float*, void*, size_t, cudaStream_t) { return -3; }
-int tc_backward_data(const Geom&, int, int, const float*, const float*, const float*, const float*, float*, float*, void*, size_t, cudaStream_t) { return -3; }
-int tc_backward_weight(const Geom&, int, int, const float*, const float*, const float*, float*, void*, size_t, cudaStream_t) { return -3; }
-int tc_check_status(cudaStream_t) { return 0; }
-int tc_launch_count(const Geom&, int, int) { return 0; }
+
+using namespace tc;
+
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kTileN = 128;            // output positions per tile
+constexpr int kTileK = 64;             // bf16 elements per K chunk (one 128-byte swizzled row)
+constexpr int kTileBytes = 128 * 128;  // one 128-row operand tile: 16 KB
+constexpr int kProducerWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kFwdThreads = 32 * (2 + kProducerWarps + kEpilogueWarps);   // MMA, loader, producers, epilogue
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct TcDims {
+    int KC;         // K chunks per group: ceil(kv*Cg / 64)
+    int MT;         // 128-row output-channel tiles per group
+    int MB;         // o-blocks per group (each up to 2 m-tiles sharing the sampled operand)
+    long long PT;   // position tiles
+};
+
+TcDims tc_dims(const Geom& g) {
+    TcDims d;
+    d.KC = (g.kv * g.Cg + kTileK - 1) / kTileK;
+    d.MT = (g.Og + 127) / 128;
+    d.MB = (d.MT + 1) / 2;
+    d.PT = (g.P + kTileN - 1) / kTileN;
+    return d;
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Pre-pass 1: NC(L)HW fp32 -> N(L)HWC bf16
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+to_channels_last_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ xcl, int C, int iv) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+    const float* xn = x + (size_t)n * C * iv;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + i * 8, p = p0 + tx;
+        tile[ty + i * 8][tx] = (c < C && p < iv) ? xn[(size_t)c * iv + p] : 0.f;
+    }
+    __syncthreads();
+    __nv_bfloat16* on = xcl + (size_t)n * iv * C;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = p0 + ty + i * 8, c = c0 + tx;
+        if (p < iv && c < C) on[(size_t)p * C + c] = __float2bfloat16_rn(tile[tx][ty + i * 8]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Pre-pass 2: weight [O, Cg, kv] fp32 -> swizzled K-major bf16 tiles [G][MT][KC][128 rows x 64 k],
+// GEMM-K index k' = tap * Cg + c.  Rows >= Og and k' >= kv*Cg are zero.
+// ---------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+pack_weight_fwd(const Geom g, const float* __restrict__ w, uint8_t* __restrict__ wpk, int MT, int KC) {
+    const int tile = blockIdx.x;                  // (j * MT + mt) * KC + kc
+    const int kc = tile % KC, mt = (tile / KC) % MT, j = tile / KC / MT;
+    uint8_t* dst = wpk + (size_t)tile * kTileBytes;
+    for (int e = threadIdx.x; e < 128 * 8; e += blockDim.x) {
+        const int row = e / 8, chunk = e % 8;
+        const int o = mt * 128 + row;
+        uint32_t pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float v[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int kp = kc * kTileK + chunk * 8 + q * 2 + h;
+                float val = 0.f;
+                if (o < g.Og && kp < g.kv * g.Cg) {
+                    const int tap = kp / g.Cg, cl = kp % g.Cg;
+                    val = w[((size_t)(j * g.Og + o) * g.Cg + cl) * g.kv + tap];
+                }
+                v[h] = val;
+            }
+            pk[q] = pack_bf16x2(v[0], v[1]);
+        }
+        *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Sampling of one 16-byte chunk (8 consecutive channels of one tap, one deformable group) at one output
+// position, from the channels-last bf16 input.  Returns 8 bf16 packed in 4 words.
+// ---------------------------------------------------------------------------------------------------
+template <int D, bool DEFORM>
+__device__ __forceinline__ uint4 sample_chunk(const Geom& g, const __nv_bfloat16* __restrict__ xcl,
+                                              const float* __restrict__ off, const OutPos& op, int tap, int c,
+                                              int grp) {
+    const __nv_bfloat16* xn = xcl + (size_t)op.n * g.iv * g.C + c;
+    if (!DEFORM) {
+        int idx;
+        if (!locate_plain<D>(g, tap, op, idx)) return make_uint4(0, 0, 0, 0);
+        return __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx * g.C));
+    }
+    Pt<float, D> s;
+    locate<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op, s);
+    if (!s.valid) return make_uint4(0, 0, 0, 0);
+    int idx[1 << D];
+    float cw[1 << D];
+    corner_indices<float, D>(g, s, idx);
+    corner_weights<float, D>(s, cw);
+    uint4 q[1 << D];
+#pragma unroll
+    for (int e = 0; e < (1 << D); ++e) q[e] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx[e] * g.C));
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+    for (int e = 0; e < (1 << D); ++e) {
+        const uint32_t wd[4] = {q[e].x, q[e].y, q[e].z, q[e].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(cw[e], bf16_lo(wd[i]), acc[2 * i]);
+            acc[2 * i + 1] = fmaf(cw[e], bf16_hi(wd[i]), acc[2 * i + 1]);
+        }
+    }
+    return make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                      pack_bf16x2(acc[6], acc[7]));
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Forward implicit GEMM.  Persistent CTAs, one per SM; warp roles:
+//   warp 0      MMA issue (one elected lane) and tensor-memory allocation
+//   warp 1      weight-tile loader (bulk async copies, one elected lane)
+//   warps 2-9   producers: sample the input patch tile straight into the swizzled B operand
+//   warps 10-13 epilogue: tensor memory -> registers -> (+bias) -> y
+// Tile = (conv group, block of up to 256 output channels, 128 output positions).  The sampled operand of a
+// K chunk is shared by both 128-row halves of the output-channel block.
+// ---------------------------------------------------------------------------------------------------
+struct FwdSmem {
+    // per stage: A0 | A1 | B, 16 KB each
+    static constexpr int kStageBytes = 3 * kTileBytes;
+    static constexpr int kBarOffset = kStages * kStageBytes;
+    // barriers: full[S], empty[S], acc_full[2], acc_empty[2]; then the tensor-memory base address
+    static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
+};
+
+template <int D, bool DEFORM>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
+                  const uint8_t* __restrict__ wpk, const float* __restrict__ bias, float* __restrict__ y,
+                  const int KC, const int MT, const int MB, const long long PT) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBarOffset);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], kProducerWarps * 32 + 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], kEpilogueWarps * 32);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long n_tiles = (long long)g.G * MB * PT;
+    constexpr uint32_t kIdesc = make_idesc(128, kTileN, 0, 0);
+
+    if (warp == 0) {
+        // ------------------------------------------------ MMA issue
+        if (lane == 0) {
+            uint32_t it = 0, tl = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
+                const int mb = (int)((t / PT) % MB);
+                const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                const uint32_t b = tl & 1;
+                ok = mbar_wait(&acc_empty[b], ((tl >> 1) & 1) ^ 1);
+                tc_fence_after();
+                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                    const uint32_t s = it % kStages;
+                    ok = mbar_wait(&full[s], (it / kStages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(smem + s * FwdSmem::kStageBytes);
+                    const uint32_t b_base = a_base + 2 * kTileBytes;
+                    for (int mt = 0; mt < mtb; ++mt) {
+#pragma unroll
+                        for (int k = 0; k < kTileK / 16; ++k) {
+                            const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
+                            const uint64_t bd = make_desc(b_base + k * 32, 16, 1024);
+                            umma_bf16(tmem_base + b * 256 + mt * 128, ad, bd, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[b]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ weight loader
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int mb = (int)((t / PT) % MB);
+                const int j = (int)(t / PT / MB);
+                const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                    const uint32_t s = it % kStages;
+                    ok = mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&full[s], (uint32_t)(mtb * kTileBytes));
+                    for (int mt = 0; mt < mtb; ++mt) {
+                        const uint8_t* src = wpk + ((size_t)(j * MT + mb * 2 + mt) * KC + kc) * kTileBytes;
+                        bulk_g2s(smem + s * FwdSmem::kStageBytes + mt * kTileBytes, src, kTileBytes, &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp < 2 + kProducerWarps) {
+        // ------------------------------------------------ producers
+        const int ptid = threadIdx.x - 64;          // 0..255
+        const int chunk = ptid % 8;                 // 16-byte chunk of the 128-byte row
+        const int row0 = ptid / 8;                  // rows row0 + 32*i
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            const long long pt = t % PT;
+            const int j = (int)(t / PT / MB);
+            OutPos op[4];
+            bool pok[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const long long P = pt * kTileN + row0 + 32 * i;
+                pok[i] = P < g.P;
+                op[i] = decompose_pos(g, pok[i] ? P : 0);
+            }
+            for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                const uint32_t s = it % kStages;
+                const int kp = kc * kTileK + chunk * 8;
+                const bool kok = kp < g.kv * g.Cg;
+                uint32_t tap = 0, cl = 0;
+                g.d_Cg.divmod((uint32_t)(kok ? kp : 0), tap, cl);
+                const int c = j * g.Cg + (int)cl;
+                const int grp = (int)g.d_cpg.div((uint32_t)c);
+                uint4 v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    v[i] = make_uint4(0, 0, 0, 0);
+                    if (kok && pok[i]) v[i] = sample_chunk<D, DEFORM>(g, xcl, off, op[i], (int)tap, c, grp);
+                }
+                ok = mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1);
+                if (!ok) break;
+                const uint32_t b_base = smem_u32(smem + s * FwdSmem::kStageBytes + 2 * kTileBytes);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    st_shared_v4(b_base + swz_offset(row0 + 32 * i, chunk), v[i].x, v[i].y, v[i].z, v[i].w);
+                fence_proxy_async_smem();
+                mbar_arrive(&full[s]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue
+        const int q = warp & 3;                     // tensor-memory lane quarter this warp may access
+        uint32_t tl = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
+            const long long pt = t % PT;
+            const int mb = (int)((t / PT) % MB);
+            const int j = (int)(t / PT / MB);
+            const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+            const uint32_t b = tl & 1;
+            ok = mbar_wait(&acc_full[b], (tl >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            for (int mt = 0; mt < mtb; ++mt) {
+                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;      // output channel within the group
+                const bool o_ok = ol < g.Og;
+                const int o = j * g.Og + ol;
+                const float bv = (bias != nullptr && o_ok) ? __ldg(bias + o) : 0.f;
+#pragma unroll 1
+                for (int cc = 0; cc < kTileN / 32; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 256 + mt * 128 + cc * 32, v);
+                    tmem_ld_wait();
+                    const long long P0 = pt * kTileN + cc * 32;
+                    if (!o_ok || P0 >= g.P) continue;
+                    uint32_t n0, opos0;
+                    g.d_ov.divmod((uint32_t)P0, n0, opos0);
+                    float* dst = y + ((size_t)n0 * g.O + o) * g.ov + opos0;
+                    const bool fast = (opos0 + 32 <= (uint32_t)g.ov) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                    if (fast) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(dst + 4 * i) =
+                                make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
+                                            __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const long long P = P0 + i;
+                            if (P < g.P) {
+                                uint32_t n, opos;
+                                g.d_ov.divmod((uint32_t)P, n, opos);
+                                y[((size_t)n * g.O + o) * g.ov + opos] = __uint_as_float(v[i]) + bv;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[b]);
+        }
+    }
+
+    // teardown: every role has left its loop (normally or after a bounded wait gave up)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int sm_count() {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+}
+
+template <int D, bool DEFORM>
+int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* wpk,
+                      const float* bias, float* y, cudaStream_t st) {
+    const TcDims d = tc_dims(g);
+    const int smem = FwdSmem::kTotal + 1024;
+    auto kern = tc_forward_kernel<D, DEFORM>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
+    const long long tiles = (long long)g.G * d.MB * d.PT;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, kFwdThreads, smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+struct FwdWorkspace {
+    size_t xcl_off, xcl_bytes, wpk_off, wpk_bytes, total;
+};
+FwdWorkspace fwd_workspace(const Geom& g) {
+    const TcDims d = tc_dims(g);
+    FwdWorkspace w;
+    w.xcl_off = 0;
+    w.xcl_bytes = align_up((size_t)g.N * g.iv * g.C * 2, 256);
+    w.wpk_off = w.xcl_bytes;
+    w.wpk_bytes = align_up((size_t)g.G * d.MT * d.KC * kTileBytes, 256);
+    w.total = w.wpk_off + w.wpk_bytes;
+    return w;
+}
+
+int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cudaStream_t st) {
+    dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+    to_channels_last_bf16<<<grid, 256, 0, st>>>(x, xcl, g.C, g.iv);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+bool tc_supported(const Geom& g, int ndim, int deform) {
+    (void)ndim;
+    if (g.Cg % 8 != 0) return false;
+    if (deform && g.cpg % 8 != 0) return false;
+    if (g.N > 65535) return false;
+    return true;
+}
+
+size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
+    (void)ndim;
+    if (pass == 0) return fwd_workspace(g).total;
+    return 0;
+}
+
+int tc_launch_count(const Geom& g, int ndim, int pass) {
+    (void)g; (void)ndim;
+    if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
+    return 1;
+}
+
+int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+               const float* bias, float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+    const FwdWorkspace l = fwd_workspace(g);
+    if (ws_bytes < l.total) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+    uint8_t* wpk = base + l.wpk_off;
+    const TcDims d = tc_dims(g);
+    int r = launch_channels_last(g, x, xcl, st);
+    if (r != 0) return r;
+    pack_weight_fwd<<<g.G * d.MT * d.KC, 256, 0, st>>>(g, w, wpk, d.MT, d.KC);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (ndim == 2) return deform ? launch_tc_forward<2, true>(g, xcl, off, wpk, bias, y, st)
+                                 : launch_tc_forward<2, false>(g, xcl, off, wpk, bias, y, st);
+    return deform ? launch_tc_forward<3, true>(g, xcl, off, wpk, bias, y, st)
+                  : launch_tc_forward<3, false>(g, xcl, off, wpk, bias, y, st);
+}
+
+int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+                     const float* dy, float* dx, float* doff, void* ws, size_t ws_bytes, cudaStream_t st) {
+    (void)ws; (void)ws_bytes;
+    return simt_backward_data(g, 0, ndim, deform, x, off, w, dy, dx, deform ? doff : nullptr, st);
+}
+
+int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* dy,
+                       float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
+    (void)ws; (void)ws_bytes;
+    return simt_backward_weight(g, 0, ndim, deform, x, off, dy, dw, st);
+}
+
+int tc_check_status(cudaStream_t st) {
+    if (cudaStreamSynchronize(st) != cudaSuccess) return -5;
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v)) != cudaSuccess) return -5;
+    if (v != 0) {
+        const unsigned int z = 0;
+        cudaMemcpyToSymbol(g_tc_status, &z, sizeof(z));
+        return -6;
+    }
+    return 0;
+}
+
+}  // namespace dcn
