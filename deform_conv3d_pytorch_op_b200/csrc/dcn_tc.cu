@@ -396,6 +396,36 @@ int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cuda
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+#include "dcn_tc_wgrad.cuh"
+#include "dcn_tc_dgrad.cuh"
+
+struct BwdWeightWorkspace {
+    size_t xcl_off, dpk_off, total;
+};
+BwdWeightWorkspace bwd_weight_workspace(const Geom& g) {
+    const WgDims d = wg_dims(g);
+    BwdWeightWorkspace w;
+    w.xcl_off = 0;
+    w.dpk_off = align_up((size_t)g.N * g.iv * g.C * 2, 256);
+    w.total = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC * kTileBytes, 256);
+    return w;
+}
+
+struct BwdDataWorkspace {
+    size_t xcl_off, dpk_off, wpk_off, dxcl_off, dxcl_bytes, total;
+};
+BwdDataWorkspace bwd_data_workspace(const Geom& g) {
+    const DgDims d = dg_dims(g);
+    BwdDataWorkspace w;
+    w.xcl_off = 0;
+    w.dpk_off = align_up((size_t)g.N * g.iv * g.C * 2, 256);
+    w.wpk_off = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC2 * kTileBytes, 256);
+    w.dxcl_off = w.wpk_off + align_up((size_t)g.G * d.NB * d.OC * 2 * kTileBytes, 256);
+    w.dxcl_bytes = align_up((size_t)g.N * g.iv * g.C * 4, 256);
+    w.total = w.dxcl_off + w.dxcl_bytes;
+    return w;
+}
+
 }  // namespace
 
 bool tc_supported(const Geom& g, int ndim, int deform) {
@@ -409,13 +439,15 @@ bool tc_supported(const Geom& g, int ndim, int deform) {
 size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
     (void)ndim;
     if (pass == 0) return fwd_workspace(g).total;
-    return 0;
+    if (pass == 1) return bwd_data_workspace(g).total;
+    return bwd_weight_workspace(g).total;
 }
 
 int tc_launch_count(const Geom& g, int ndim, int pass) {
     (void)g; (void)ndim;
     if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
-    return 1;
+    if (pass == 1) return 5;      // channels-last copy, dy pack, weight pack, implicit GEMM + scatter, dx transpose-add
+    return 3;                     // channels-last copy, dy pack, implicit GEMM
 }
 
 int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
@@ -438,14 +470,56 @@ int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float*
 
 int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
                      const float* dy, float* dx, float* doff, void* ws, size_t ws_bytes, cudaStream_t st) {
-    (void)ws; (void)ws_bytes;
-    return simt_backward_data(g, 0, ndim, deform, x, off, w, dy, dx, deform ? doff : nullptr, st);
+    const BwdDataWorkspace l = bwd_data_workspace(g);
+    if (ws_bytes < l.total) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+    uint8_t* dpk = base + l.dpk_off;
+    uint8_t* wpk = base + l.wpk_off;
+    float* dxcl = dx != nullptr ? reinterpret_cast<float*>(base + l.dxcl_off) : nullptr;
+    if (!deform) doff = nullptr;
+    const DgDims d = dg_dims(g);
+    int r = 0;
+    if (deform) {
+        r = launch_channels_last(g, x, xcl, st);
+        if (r != 0) return r;
+    }
+    pack_dy<<<dim3((unsigned)d.PC2, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC2);
+    pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (dxcl != nullptr && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
+    if (doff != nullptr &&
+        cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * ndim * g.ov * sizeof(float), st) != cudaSuccess)
+        return -5;
+    if (ndim == 2) r = deform ? launch_tc_dgrad<2, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
+                              : launch_tc_dgrad<2, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+    else r = deform ? launch_tc_dgrad<3, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
+                    : launch_tc_dgrad<3, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+    if (r != 0) return r;
+    if (dx != nullptr) {
+        dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+        add_from_channels_last<<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+    }
+    return 0;
 }
 
 int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* dy,
                        float* dw, void* ws, size_t ws_bytes, cudaStream_t st) {
-    (void)ws; (void)ws_bytes;
-    return simt_backward_weight(g, 0, ndim, deform, x, off, dy, dw, st);
+    const BwdWeightWorkspace l = bwd_weight_workspace(g);
+    if (ws_bytes < l.total) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+    uint8_t* dpk = base + l.dpk_off;
+    const WgDims d = wg_dims(g);
+    int r = launch_channels_last(g, x, xcl, st);
+    if (r != 0) return r;
+    pack_dy<<<dim3((unsigned)d.PC, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (ndim == 2) return deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dw, st)
+                                 : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dw, st);
+    return deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dw, st)
+                  : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
 }
 
 int tc_check_status(cudaStream_t st) {
