@@ -151,6 +151,25 @@ int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const v
     return dcn::simt_forward(g, p->dtype, p->ndim, p->deformable, x, offset, weight, bias, y, st);
 }
 
+size_t dcn_static_scratch_bytes(void) { return dcn::tc_static_scratch_bytes(); }
+
+int dcn_forward_static_scratch(const dcn_problem* p, const void* x, const void* offset, const void* weight,
+                               const void* bias, void* y, void* stream) {
+    const int v = validate(p);
+    if (v != DCN_OK) return v;
+    if (p->precision != DCN_PREC_BF16) return DCN_ERR_UNSUPPORTED;     // the EXACT path has no scratch to replace
+    if (x == nullptr || weight == nullptr || y == nullptr || (p->deformable && offset == nullptr)) return DCN_ERR_NULL;
+    const int a = check_ptrs(p, {x, offset, weight, bias, y});
+    if (a != DCN_OK) return a;
+    Geom g;
+    make_geom(p, g);
+    if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
+    if (dcn::tc_workspace_bytes(g, p->ndim, DCN_PASS_FORWARD) > dcn::tc_static_scratch_bytes()) return DCN_ERR_LIMIT;
+    return dcn::tc_forward_static(g, p->ndim, p->deformable, (const float*)x, (const float*)offset,
+                                  (const float*)weight, (const float*)bias, (float*)y,
+                                  static_cast<cudaStream_t>(stream));
+}
+
 int dcn_backward_data(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* dy,
                       void* dx, void* doffset, void* ws, size_t ws_bytes, void* stream) {
     const int v = validate(p);

@@ -522,6 +522,35 @@ int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, cons
                   : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Forward pass for callers that must not allocate: the scratch (channels-last bf16 copy of the input and
+// the packed weight tiles) lives in a fixed array that is part of the library image instead of a
+// caller-provided workspace.  Every device that loads the library holds kStaticScratchBytes until the
+// process exits.  In host code the array's name is only a stand-in for the symbol; the device address is
+// obtained once per device with cudaGetSymbolAddress while that device is current.
+// ---------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+size_t tc_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+                      const float* bias, float* y, cudaStream_t st) {
+    constexpr int kMaxDevices = 64;
+    static void* volatile scratch_of_device[kMaxDevices] = {};
+    if (fwd_workspace(g).total > kStaticScratchBytes) return -8;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -5;
+    if (dev < 0 || dev >= kMaxDevices) return -8;
+    void* ptr = scratch_of_device[dev];
+    if (ptr == nullptr) {
+        // first call on this device: resolve the array's device address (may load the module)
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return -5;
+        scratch_of_device[dev] = ptr;      // racing first calls resolve the same address
+    }
+    return tc_forward(g, ndim, deform, x, off, w, bias, y, ptr, kStaticScratchBytes, st);
+}
+
 int tc_check_status(cudaStream_t st) {
     if (cudaStreamSynchronize(st) != cudaSuccess) return -5;
     unsigned int v = 0;

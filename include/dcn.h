@@ -103,6 +103,23 @@ int dcn_launch_count(const dcn_problem* p, int pass);
 int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* bias,
                 void* y, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Forward pass that allocates nothing and needs no workspace (no counterpart in the reference, which
+ * leaves all allocation to its Python layer).  It is for callers that cannot hand over scratch memory:
+ * code running where device allocation is forbidden or would stall the pipeline -- an inference plugin's
+ * enqueue hook, a real-time loop, a process whose memory pool already owns the whole device.
+ * Same arithmetic and results as dcn_forward with precision DCN_PREC_BF16 (other precisions are refused
+ * with DCN_ERR_UNSUPPORTED).  The scratch is a fixed array inside the library image of
+ * dcn_static_scratch_bytes() bytes (32 MiB), held on every device that loads the library until the process
+ * exits; a problem whose forward workspace (dcn_workspace_bytes) exceeds it is refused with DCN_ERR_LIMIT
+ * before anything is launched.  The first call on each device resolves the array's device address (this
+ * may load the library's device code), so make that first call outside any stream capture.  All calls on a
+ * device share the one array, which keeps the previous call's contents; this pass overwrites every byte it
+ * later reads, so nothing needs clearing, but two calls whose kernels overlap on the GPU (different
+ * streams, or different host threads) race on it: serialise them. */
+size_t dcn_static_scratch_bytes(void);
+int dcn_forward_static_scratch(const dcn_problem* p, const void* x, const void* offset, const void* weight,
+                               const void* bias, void* y, void* stream);
+
 /* Gradients w.r.t. input and offset.  Either of dx / doffset may be NULL (not wanted).
  * dx ACCUMULATES into the caller's buffer (zero it first, as the reference's Python does,
  * deform_conv3d_function.py:53); doffset is OVERWRITTEN (reference kernel stores with `=`).
