@@ -86,19 +86,18 @@ __device__ __forceinline__ void decompose_tap(const Geom& g, int tap, int t[3]) 
     t[0] = (int)tl; t[1] = (int)th; t[2] = (int)tw;
 }
 
-// Locate one sampling point.  off_n points at the sample's offset block [dg*kv*D, ov].
+// Locate one sampling point from its D offset values (axis order (l,) h, w).
 template <typename T, int D>
-__device__ __forceinline__ void locate(const Geom& g, const T* __restrict__ off_n, int grp, int tap,
-                                       const OutPos& op, Pt<T, D>& s) {
+__device__ __forceinline__ void locate_with(const Geom& g, const T (&offv)[D], int tap, const OutPos& op,
+                                            Pt<T, D>& s) {
     int t[3];
     decompose_tap(g, tap, t);
-    const T* ob = off_n + ((size_t)(grp * g.kv + tap) * D) * g.ov + op.opos;
     bool ok = true;
 #pragma unroll
     for (int a = 0; a < D; ++a) {
         const int ax = a + (3 - D);
         const int ib = op.base[ax] + t[ax] * g.dil[ax];
-        const T pd = (T)ib + __ldg(ob + (size_t)a * g.ov);       // single rounding, no multiply
+        const T pd = (T)ib + offv[a];                            // single rounding, no multiply
         s.p[a] = pd;
         ok = ok && (pd > (T)-1) && (pd < (T)g.in[ax]);
     }
@@ -116,6 +115,24 @@ __device__ __forceinline__ void locate(const Geom& g, const T* __restrict__ off_
             s.hw[a] = (T)1 - s.lw[a];
         }
     }
+}
+
+// Address of the first offset component of (grp, tap) at this output position; components are ov apart.
+template <typename T, int D>
+__device__ __forceinline__ const T* offset_ptr(const Geom& g, const T* __restrict__ off_n, int grp, int tap,
+                                               const OutPos& op) {
+    return off_n + ((size_t)(grp * g.kv + tap) * D) * g.ov + op.opos;
+}
+
+// Locate one sampling point.  off_n points at the sample's offset block [dg*kv*D, ov].
+template <typename T, int D>
+__device__ __forceinline__ void locate(const Geom& g, const T* __restrict__ off_n, int grp, int tap,
+                                       const OutPos& op, Pt<T, D>& s) {
+    const T* ob = offset_ptr<T, D>(g, off_n, grp, tap, op);
+    T offv[D];
+#pragma unroll
+    for (int a = 0; a < D; ++a) offv[a] = __ldg(ob + (size_t)a * g.ov);
+    locate_with<T, D>(g, offv, tap, op, s);
 }
 
 // Integer tap location of the plain convolution (conv2d/lib/conv2d_cuda_kernel.cu:60-67).

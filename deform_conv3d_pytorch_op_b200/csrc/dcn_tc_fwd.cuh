@@ -1,0 +1,421 @@
+// Forward implicit GEMM on tcgen05 (included by dcn_tc.cu inside its anonymous namespace).
+//
+//   y[o, P] = sum over k' of W[o, k'] * sample(k', P)  (+ bias)            k' = tap * Cg + c
+//
+// Persistent CTAs, one per SM; 16 warps:
+//   warp 0       MMA issue (one elected lane) and tensor-memory allocation
+//   warp 1       weight-tile loader (bulk async copies, one elected lane)
+//   warps 2-3    coordinate warps (dcn_tc_sampler.cuh)
+//   warps 4-11   gather warps: build the sampled, interpolated patch tile straight into the swizzled B operand
+//   warps 12-15  epilogue: tensor memory -> registers -> (+bias) -> y
+// Tile = (conv group, block of up to 256 output channels, 128 output positions).  The sampled operand of a
+// K chunk is shared by both 128-row halves of the output-channel block.
+#pragma once
+
+constexpr int kMaxStages = 4;
+constexpr int kCoordWarps = 2;
+constexpr int kGatherWarps = 8;
+constexpr int kFwdThreads = 32 * (2 + kCoordWarps + kGatherWarps + kEpilogueWarps);
+constexpr int kFwdStageBytes = 3 * kTileBytes;      // A0 | A1 | B
+constexpr int kSmemLimit = 232448;                   // 227 KB opt-in maximum per CTA
+
+constexpr int kMaxTabs = 3;
+constexpr int kOffRing = 3;          // offset prefetch distance of the coordinate warps + 1
+
+struct FwdCtl {            // lives behind the stages, the tables and the offset staging ring
+    uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2], tab_full[kMaxTabs], tab_empty[kMaxTabs];
+    uint32_t tmem_base;
+    int slot_of_chunk[kMaxTabs][8];
+};
+
+template <int D, bool DEFORM>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
+                  const uint8_t* __restrict__ wpk, const float* __restrict__ bias, float* __restrict__ y,
+                  const int KC, const int MT, const int MB, const long long PT, const int n_stages,
+                  const int max_slots, const int n_tabs) {
+    using Entry = TabEntry<D, DEFORM>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Entry* tab = reinterpret_cast<Entry*>(smem + n_stages * kFwdStageBytes);          // [n_tabs][max_slots][128]
+    float* ostage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tab) +
+                                             (size_t)n_tabs * max_slots * 128 * sizeof(Entry));   // [3][max_slots][D][128]
+    FwdCtl* ctl = reinterpret_cast<FwdCtl*>(ostage + (size_t)kOffRing * max_slots * D * 128);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(&ctl->full[s], kGatherWarps * 32 + 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], kEpilogueWarps * 32);
+        }
+        for (int b = 0; b < kMaxTabs; ++b) {
+            mbar_init(&ctl->tab_full[b], kCoordWarps * 32);
+            mbar_init(&ctl->tab_empty[b], kGatherWarps * 32);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&ctl->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const long long n_tiles = (long long)g.G * MB * PT;
+    constexpr uint32_t kIdesc = make_idesc(128, kTileN, 0, 0);
+
+    if (warp == 0) {
+        // ------------------------------------------------ MMA issue
+        if (lane == 0) {
+            uint32_t it = 0, tl = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
+                const int mb = (int)((t / PT) % MB);
+                const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                const uint32_t b = tl & 1;
+                ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
+                tc_fence_after();
+                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                    const uint32_t s = it % n_stages;
+                    ok = mbar_wait(&ctl->full[s], (it / n_stages) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(smem + s * kFwdStageBytes);
+                    const uint32_t b_base = a_base + 2 * kTileBytes;
+                    for (int mt = 0; mt < mtb; ++mt) {
+#pragma unroll
+                        for (int k = 0; k < kTileK / 16; ++k) {
+                            const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
+                            const uint64_t bd = make_desc(b_base + k * 32, 16, 1024);
+                            umma_bf16(tmem_base + b * 256 + mt * 128, ad, bd, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&ctl->empty[s]);
+                }
+                if (ok) umma_commit(&ctl->acc_full[b]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ weight loader
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int mb = (int)((t / PT) % MB);
+                const int j = (int)(t / PT / MB);
+                const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                    const uint32_t s = it % n_stages;
+                    ok = mbar_wait(&ctl->empty[s], ((it / n_stages) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)(mtb * kTileBytes));
+                    for (int mt = 0; mt < mtb; ++mt) {
+                        const uint8_t* src = wpk + ((size_t)(j * MT + mb * 2 + mt) * KC + kc) * kTileBytes;
+                        bulk_g2s(smem + s * kFwdStageBytes + mt * kTileBytes, src, kTileBytes, &ctl->full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp < 2 + kCoordWarps) {
+        // ------------------------------------------------ coordinate warps
+        // Offsets are prefetched two stages ahead with 4-byte cp.async into a private staging ring, so the
+        // offset-load latency never sits on the critical path of a stage.
+        const int ctid = threadIdx.x - 64;          // 0..63, rows ctid and ctid + 64
+        struct Cur {
+            long long t;
+            int kc, j;
+            OutPos op[2];
+            bool pok[2];
+        };
+        auto init_tile = [&](Cur& c) {
+            const long long pt = c.t % PT;
+            c.j = (int)(c.t / PT / MB);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const long long P = pt * kTileN + ctid + 64 * i;
+                c.pok[i] = P < g.P;
+                c.op[i] = decompose_pos(g, c.pok[i] ? P : 0);
+            }
+        };
+        auto advance = [&](Cur& c) {
+            if (c.t >= n_tiles) return;
+            if (++c.kc == KC) {
+                c.kc = 0;
+                c.t += gridDim.x;
+                if (c.t < n_tiles) init_tile(c);
+            }
+        };
+        auto stage_slots = [&](const Cur& c) {
+            int tap_, c_;
+            const int key = chunk_key(g, c.j, c.kc * kTileK + (lane & 7) * 8, tap_, c_);
+            return make_slots(key, lane, 8);
+        };
+        auto prefetch = [&](const Cur& c, uint32_t itp) {
+            if (DEFORM && c.t < n_tiles) {
+                const SlotInfo si = stage_slots(c);
+                float* dst = ostage + (size_t)(itp % kOffRing) * max_slots * D * 128;
+                for (int sl = 0; sl < si.nslots; ++sl) {
+                    const int key = slot_key(si, sl);
+                    if (key < 0) continue;
+                    const int grp = key / g.kv, tap = key - grp * g.kv;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        if (!c.pok[i]) continue;
+                        const float* src = offset_ptr<float, D>(g, off + (size_t)c.op[i].n * g.dg * g.kv * D * g.ov,
+                                                                grp, tap, c.op[i]);
+#pragma unroll
+                        for (int a = 0; a < D; ++a)
+                            cp_async4(dst + (size_t)(sl * D + a) * 128 + ctid + 64 * i, src + (size_t)a * g.ov);
+                    }
+                }
+            }
+            cp_async_commit();
+        };
+        Cur cur, pre;
+        cur.t = blockIdx.x; cur.kc = 0;
+        if (cur.t < n_tiles) init_tile(cur);
+        pre = cur;
+        prefetch(pre, 0); advance(pre);
+        prefetch(pre, 1); advance(pre);
+        uint32_t it = 0;
+        bool ok = true;
+        while (cur.t < n_tiles && ok) {
+            prefetch(pre, it + 2); advance(pre);
+            cp_async_wait<2>();
+            const uint32_t tb = it % n_tabs;
+            const SlotInfo si = stage_slots(cur);
+            ok = mbar_wait(&ctl->tab_empty[tb], ((it / n_tabs) & 1) ^ 1);
+            if (!ok) break;
+            if (warp == 2 && lane < 8) ctl->slot_of_chunk[tb][lane] = si.my_slot;
+            const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 128;
+            for (int sl = 0; sl < si.nslots; ++sl) {
+                const int key = slot_key(si, sl);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float offv[D];
+#pragma unroll
+                    for (int a = 0; a < D; ++a)
+                        offv[a] = (DEFORM && key >= 0 && cur.pok[i]) ? src[(size_t)(sl * D + a) * 128 + ctid + 64 * i] : 0.f;
+                    fill_entry_from<D, DEFORM>(g, offv, cur.op[i], cur.pok[i], key,
+                                               tab + ((size_t)tb * max_slots + sl) * 128 + ctid + 64 * i);
+                }
+            }
+            mbar_arrive(&ctl->tab_full[tb]);
+            advance(cur);
+            ++it;
+        }
+        cp_async_wait<0>();
+    } else if (warp < 2 + kCoordWarps + kGatherWarps) {
+        // ------------------------------------------------ gather warps
+        // A stage is produced in passes of RPP rows per thread; the loads of the next pass are in flight while
+        // the current pass is interpolated and stored, across stage and tile boundaries.
+        const int gtid = threadIdx.x - 32 * (2 + kCoordWarps);   // 0..255
+        const int chunk = gtid % 8;                 // 16-byte chunk of the 128-byte row
+        const int row0 = gtid / 8;                  // rows row0 + 32*i, i = 0..3
+        constexpr int NQ = DEFORM ? (1 << D) : 1;
+        constexpr int RPP = (D == 2 || !DEFORM) ? 2 : 1;          // rows per pass
+        constexpr int PPS = 4 / RPP;                               // passes per stage
+        struct Pass {
+            uint4 q[RPP][NQ];
+            float w[RPP][NQ];
+            uint32_t it;
+            int h;
+        };
+        // issue cursor
+        long long ct = blockIdx.x;
+        int ckc = 0, ch = 0, cj = 0, cc = 0, csl = 0;
+        uint32_t cit = 0;
+        size_t nbase[4];
+        bool failed = false;
+        auto init_tile = [&]() {
+            const long long pt = ct % PT;
+            cj = (int)(ct / PT / MB);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const long long P = pt * kTileN + row0 + 32 * i;
+                uint32_t n = 0, opos = 0;
+                if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
+                nbase[i] = (size_t)n * g.iv * g.C;
+            }
+        };
+        if (ct < n_tiles) init_tile();
+        auto issue = [&](Pass& p) -> bool {
+            if (ct >= n_tiles || failed) return false;
+            const uint32_t tb = cit % n_tabs;
+            if (ch == 0) {
+                if (!mbar_wait(&ctl->tab_full[tb], (cit / n_tabs) & 1)) { failed = true; return false; }
+                csl = ctl->slot_of_chunk[tb][chunk];
+                const int kp = ckc * kTileK + chunk * 8;
+                uint32_t tap, cl;
+                g.d_Cg.divmod((uint32_t)(kp < g.kv * g.Cg ? kp : 0), tap, cl);
+                cc = cj * g.Cg + (int)cl;
+            }
+            const Entry* trow = tab + ((size_t)tb * max_slots + csl) * 128;
+#pragma unroll
+            for (int r = 0; r < RPP; ++r) {
+#pragma unroll
+                for (int hh = 0; hh < PPS; ++hh) {
+                    if (hh == ch) {
+                        const int i = hh * RPP + r;
+                        gather_issue_w<D, DEFORM>(trow + row0 + 32 * i, xcl + nbase[i] + cc, g.C, p.q[r], p.w[r]);
+                    }
+                }
+            }
+            p.it = cit;
+            p.h = ch;
+            if (ch == PPS - 1) mbar_arrive(&ctl->tab_empty[tb]);     // this thread is done with the stage's table
+            if (++ch == PPS) {
+                ch = 0;
+                ++cit;
+                if (++ckc == KC) {
+                    ckc = 0;
+                    ct += gridDim.x;
+                    if (ct < n_tiles) init_tile();
+                }
+            }
+            return true;
+        };
+        auto finish = [&](Pass& p) -> bool {
+            const uint32_t s = p.it % n_stages;
+            if (p.h == 0) {
+                if (!mbar_wait(&ctl->empty[s], ((p.it / n_stages) & 1) ^ 1)) { failed = true; return false; }
+            }
+            const uint32_t b_base = smem_u32(smem + s * kFwdStageBytes + 2 * kTileBytes);
+#pragma unroll
+            for (int r = 0; r < RPP; ++r) {
+                const uint4 v = gather_finish_w<D, DEFORM>(p.q[r], p.w[r]);
+                st_shared_v4(b_base + swz_offset(row0 + 32 * (p.h * RPP + r), chunk), v.x, v.y, v.z, v.w);
+            }
+            if (p.h == PPS - 1) {
+                fence_proxy_async_smem();
+                mbar_arrive(&ctl->full[s]);
+            }
+            return true;
+        };
+        Pass pa, pb;
+        bool ha = issue(pa);
+        while (ha) {
+            const bool hb = issue(pb);
+            if (!finish(pa)) break;
+            if (!hb) break;
+            ha = issue(pa);
+            if (!finish(pb)) break;
+        }
+    } else {
+        // ------------------------------------------------ epilogue
+        const int q = warp & 3;                     // tensor-memory lane quarter this warp may access
+        uint32_t tl = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
+            const long long pt = t % PT;
+            const int mb = (int)((t / PT) % MB);
+            const int j = (int)(t / PT / MB);
+            const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+            const uint32_t b = tl & 1;
+            ok = mbar_wait(&ctl->acc_full[b], (tl >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            for (int mt = 0; mt < mtb; ++mt) {
+                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;      // output channel within the group
+                const bool o_ok = ol < g.Og;
+                const int o = j * g.Og + ol;
+                const float bv = (bias != nullptr && o_ok) ? __ldg(bias + o) : 0.f;
+#pragma unroll 1
+                for (int cc = 0; cc < kTileN / 32; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 256 + mt * 128 + cc * 32, v);
+                    tmem_ld_wait();
+                    const long long P0 = pt * kTileN + cc * 32;
+                    if (!o_ok || P0 >= g.P) continue;
+                    uint32_t n0, opos0;
+                    g.d_ov.divmod((uint32_t)P0, n0, opos0);
+                    float* dst = y + ((size_t)n0 * g.O + o) * g.ov + opos0;
+                    const bool fast = (opos0 + 32 <= (uint32_t)g.ov) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                    if (fast) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(dst + 4 * i) =
+                                make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
+                                            __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const long long P = P0 + i;
+                            if (P < g.P) {
+                                uint32_t n, opos;
+                                g.d_ov.divmod((uint32_t)P, n, opos);
+                                y[((size_t)n * g.O + o) * g.ov + opos] = __uint_as_float(v[i]) + bv;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&ctl->acc_empty[b]);
+        }
+    }
+
+    // teardown: every role has left its loop (normally or after a bounded wait gave up)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Largest number of distinct (deformable group, tap) keys any 64-wide K chunk touches.
+inline int max_slots_per_chunk(const Geom& g, int cols_per_chunk) {
+    const int kq = g.kv * g.Cg;
+    int best = 1;
+    for (int j = 0; j < g.G; ++j) {
+        for (int k0 = 0; k0 < kq; k0 += cols_per_chunk * 8) {
+            int slots = 0, prev = -2;
+            for (int c8 = 0; c8 < cols_per_chunk; ++c8) {
+                const int kp = k0 + c8 * 8;
+                int key = -1;
+                if (kp < kq) {
+                    const int tap = kp / g.Cg, cl = kp % g.Cg;
+                    key = ((j * g.Cg + cl) / g.cpg) * g.kv + tap;
+                }
+                if (c8 == 0 || key != prev) ++slots;
+                prev = key;
+            }
+            if (slots > best) best = slots;
+        }
+    }
+    return best;
+}
+
+template <int D, bool DEFORM>
+int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* wpk,
+                      const float* bias, float* y, cudaStream_t st) {
+    const TcDims d = tc_dims(g);
+    const int max_slots = max_slots_per_chunk(g, 8);
+    const size_t tab_one = (size_t)max_slots * 128 * sizeof(TabEntry<D, DEFORM>);
+    const size_t ost_bytes = (size_t)kOffRing * max_slots * D * 128 * sizeof(float);
+    int n_tabs = kMaxTabs;
+    size_t fixed = n_tabs * tab_one + ost_bytes + sizeof(FwdCtl) + 1024;
+    if ((kSmemLimit - (long long)fixed) / kFwdStageBytes < kMaxStages) {       // big tables: two buffers instead of three
+        n_tabs = 2;
+        fixed = n_tabs * tab_one + ost_bytes + sizeof(FwdCtl) + 1024;
+    }
+    int stages = (int)((kSmemLimit - (long long)fixed) / kFwdStageBytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    // 3-D sampling (8 corners) is bound by loads in flight per thread, where the direct variant does better.
+    if (stages < 3 || (D == 3 && DEFORM)) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);
+    const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
+    auto kern = tc_forward_kernel<D, DEFORM>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
+    const long long tiles = (long long)g.G * d.MB * d.PT;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, kFwdThreads, smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

@@ -1,0 +1,264 @@
+// Sampling front end shared by the tensor-core forward and weight-gradient kernels (included by dcn_tc.cu
+// inside its anonymous namespace).
+//
+// Work is split between two kinds of warps so that the two dependent memory latencies of a sample (offset
+// load -> corner gathers) sit in different warps and overlap:
+//   coordinate warps  read the offsets (coalesced along positions), locate the sampling point exactly as the
+//                     reference does (fp32, one rounding) and publish, per (position row, key), the 2^D
+//                     corner indices and corner weights in a shared-memory table; a key is one
+//                     (deformable group, tap) pair, and a K chunk touches only a few distinct keys;
+//   gather warps      read a table entry (broadcast to the 8 lanes that share a row), fetch 2^D 16-byte
+//                     vectors of 8 bf16 channels from the channels-last input, interpolate in fp32 with packed
+//                     two-wide FMAs, round to bf16 and store one 16-byte chunk of the swizzled operand tile.
+#pragma once
+
+template <int D, bool DEFORM>
+struct alignas(16) TabEntry {
+    int idx[1 << D];      // linear index of each corner inside the sample's input volume; idx[0] < 0: invalid
+    float w[1 << D];      // corner weights (products of the per-axis weights)
+};
+template <int D>
+struct alignas(16) TabEntry<D, false> {
+    int idx[4];           // idx[0] = integer tap location or -1
+};
+
+// key of an 8-channel chunk column starting at GEMM-K index kp (k' = tap * Cg + c): grp * kv + tap, -1 past the end
+__device__ __forceinline__ int chunk_key(const Geom& g, int j, int kp, int& tap_out, int& c_out) {
+    if (kp >= g.kv * g.Cg) { tap_out = 0; c_out = 0; return -1; }
+    uint32_t tap, cl;
+    g.d_Cg.divmod((uint32_t)kp, tap, cl);
+    const int c = j * g.Cg + (int)cl;
+    tap_out = (int)tap;
+    c_out = c;
+    return (int)g.d_cpg.div((uint32_t)c) * g.kv + (int)tap;
+}
+
+// 4-byte asynchronous global -> shared copy (offset prefetch of the coordinate warps) and its group control.
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Keys of the chunk columns handled by lanes 0..ncols-1 of a warp, run-length numbered into slots.
+struct SlotInfo {
+    int my_key;        // key of column `lane` (lanes >= ncols: undefined)
+    uint32_t news;     // bit c set: column c starts a new slot
+    int my_slot;       // slot of column `lane`
+    int nslots;
+};
+__device__ __forceinline__ SlotInfo make_slots(int my_key, int lane, int ncols) {
+    SlotInfo r;
+    r.my_key = my_key;
+    const int prev = __shfl_up_sync(0xffffffffu, my_key, 1);
+    const bool is_new = lane < ncols && (lane == 0 || my_key != prev);
+    r.news = __ballot_sync(0xffffffffu, is_new);
+    r.my_slot = __popc(r.news & ((2u << lane) - 1u)) - 1;
+    r.nslots = __popc(r.news);
+    return r;
+}
+// key of slot sl (all lanes)
+__device__ __forceinline__ int slot_key(const SlotInfo& si, int sl) {
+    const int col = __fns(si.news, 0, sl + 1);
+    return __shfl_sync(0xffffffffu, si.my_key, col);
+}
+
+// Coordinate-warp side: fill one table entry.
+template <int D, bool DEFORM>
+__device__ __forceinline__ void fill_entry(const Geom& g, const float* __restrict__ off, const OutPos& op, bool pos_ok,
+                                           int key, TabEntry<D, DEFORM>* e) {
+    if constexpr (DEFORM) {
+        int4* ei = reinterpret_cast<int4*>(e->idx);
+        float4* ew = reinterpret_cast<float4*>(e->w);
+        Pt<float, D> s;
+        s.valid = false;
+        if (pos_ok && key >= 0) {
+            const int grp = key / g.kv, tap = key - grp * g.kv;
+            locate<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op, s);
+        }
+        int idx[1 << D];
+        float cw[1 << D];
+        if (s.valid) {
+            corner_indices<float, D>(g, s, idx);
+            corner_weights<float, D>(s, cw);
+        } else {
+#pragma unroll
+            for (int i = 0; i < (1 << D); ++i) { idx[i] = -1; cw[i] = 0.f; }
+        }
+#pragma unroll
+        for (int q = 0; q < (1 << D) / 4; ++q) {
+            ei[q] = make_int4(idx[4 * q], idx[4 * q + 1], idx[4 * q + 2], idx[4 * q + 3]);
+            ew[q] = make_float4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
+        }
+    } else {
+        int pidx = -1;
+        if (pos_ok && key >= 0) {
+            const int tap = key % g.kv;
+            int t;
+            if (locate_plain<D>(g, tap, op, t)) pidx = t;
+        }
+        *reinterpret_cast<int4*>(e->idx) = make_int4(pidx, 0, 0, 0);
+    }
+}
+
+// Same, with the D offset values already at hand (prefetched into shared memory).
+template <int D, bool DEFORM>
+__device__ __forceinline__ void fill_entry_from(const Geom& g, const float (&offv)[D], const OutPos& op, bool pos_ok,
+                                                int key, TabEntry<D, DEFORM>* e) {
+    if constexpr (DEFORM) {
+        int4* ei = reinterpret_cast<int4*>(e->idx);
+        float4* ew = reinterpret_cast<float4*>(e->w);
+        Pt<float, D> s;
+        s.valid = false;
+        if (pos_ok && key >= 0) {
+            const int grp = key / g.kv, tap = key - grp * g.kv;
+            locate_with<float, D>(g, offv, tap, op, s);
+        }
+        int idx[1 << D];
+        float cw[1 << D];
+        if (s.valid) {
+            corner_indices<float, D>(g, s, idx);
+            corner_weights<float, D>(s, cw);
+        } else {
+#pragma unroll
+            for (int i = 0; i < (1 << D); ++i) { idx[i] = -1; cw[i] = 0.f; }
+        }
+#pragma unroll
+        for (int q = 0; q < (1 << D) / 4; ++q) {
+            ei[q] = make_int4(idx[4 * q], idx[4 * q + 1], idx[4 * q + 2], idx[4 * q + 3]);
+            ew[q] = make_float4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
+        }
+    } else {
+        int pidx = -1;
+        if (pos_ok && key >= 0) {
+            const int tap = key % g.kv;
+            int t;
+            if (locate_plain<D>(g, tap, op, t)) pidx = t;
+        }
+        *reinterpret_cast<int4*>(e->idx) = make_int4(pidx, 0, 0, 0);
+    }
+}
+
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// two fp32 FMAs in one instruction (sm_100)
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Gather-warp side, step 1: issue the corner loads of one entry (8 channels starting at xn).
+template <int D, bool DEFORM>
+__device__ __forceinline__ void gather_issue(const TabEntry<D, DEFORM>& e, const __nv_bfloat16* __restrict__ xn,
+                                             int C, uint4 (&q)[DEFORM ? (1 << D) : 1]) {
+    if (e.idx[0] < 0) {
+#pragma unroll
+        for (int i = 0; i < (DEFORM ? (1 << D) : 1); ++i) q[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < (DEFORM ? (1 << D) : 1); ++i)
+        q[i] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)e.idx[i] * C));
+}
+
+// step 2: interpolate and round to 8 bf16.
+template <int D, bool DEFORM>
+__device__ __forceinline__ uint4 gather_finish(const TabEntry<D, DEFORM>& e, const uint4 (&q)[DEFORM ? (1 << D) : 1]) {
+    if constexpr (!DEFORM) return q[0];
+    else {
+        if (e.idx[0] < 0) return make_uint4(0, 0, 0, 0);
+        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            const uint64_t w2 = pack_f32x2(e.w[c], e.w[c]);
+            const uint32_t wd[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                acc[i] = ffma2(w2, pack_f32x2(bf16_lo(wd[i]), bf16_hi(wd[i])), acc[i]);
+        }
+        uint32_t out[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            unpack_f32x2(acc[i], lo, hi);
+            out[i] = pack_bf16x2(lo, hi);
+        }
+        return make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
+// Pipelined form: issue keeps only the loaded vectors and the weights; an invalid entry yields zero weights and
+// zero vectors, so the later interpolation returns exactly zero without a flag.
+template <int D, bool DEFORM>
+__device__ __forceinline__ void gather_issue_w(const TabEntry<D, DEFORM>* ep, const __nv_bfloat16* __restrict__ xn,
+                                               int C, uint4 (&q)[DEFORM ? (1 << D) : 1],
+                                               float (&w)[DEFORM ? (1 << D) : 1]) {
+    constexpr int NQ = DEFORM ? (1 << D) : 1;
+    const int4* ei = reinterpret_cast<const int4*>(ep->idx);
+    int idx[DEFORM ? (1 << D) : 4];
+#pragma unroll
+    for (int i = 0; i < (DEFORM ? (1 << D) : 4) / 4; ++i) {
+        const int4 t = ei[i];
+        idx[4 * i] = t.x; idx[4 * i + 1] = t.y; idx[4 * i + 2] = t.z; idx[4 * i + 3] = t.w;
+    }
+    if constexpr (DEFORM) {
+        const float4* ew = reinterpret_cast<const float4*>(ep->w);
+#pragma unroll
+        for (int i = 0; i < NQ / 4; ++i) {
+            const float4 t = ew[i];
+            w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+        }
+    } else {
+        w[0] = 1.f;
+    }
+    if (idx[0] < 0) {
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) q[i] = make_uint4(0, 0, 0, 0);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx[i] * C));
+    }
+}
+
+template <int D, bool DEFORM>
+__device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 << D) : 1],
+                                                 const float (&w)[DEFORM ? (1 << D) : 1]) {
+    if constexpr (!DEFORM) return q[0];
+    else {
+        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            const uint64_t w2 = pack_f32x2(w[c], w[c]);
+            const uint32_t wd[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                acc[i] = ffma2(w2, pack_f32x2(bf16_lo(wd[i]), bf16_hi(wd[i])), acc[i]);
+        }
+        uint32_t out[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            unpack_f32x2(acc[i], lo, hi);
+            out[i] = pack_bf16x2(lo, hi);
+        }
+        return make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
+template <int D, bool DEFORM>
+__device__ __forceinline__ TabEntry<D, DEFORM> load_entry(const TabEntry<D, DEFORM>* p) {
+    TabEntry<D, DEFORM> e;
+    const int4* s = reinterpret_cast<const int4*>(p);
+    int4* d = reinterpret_cast<int4*>(&e);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(TabEntry<D, DEFORM>) / 16); ++i) d[i] = s[i];
+    return e;
+}

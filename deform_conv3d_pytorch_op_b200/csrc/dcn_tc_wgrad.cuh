@@ -1,4 +1,6 @@
-// Weight gradient on tcgen05 (included by dcn_tc.cu inside its anonymous namespace).
+// Weight gradient on tcgen05, direct-sampling variant (included by dcn_tc.cu inside its anonymous namespace):
+// each producer thread locates its own sampling points.  Fallback of dcn_tc_wgrad2.cuh for problems whose
+// coordinate table does not fit in shared memory; also defines pack_dy and the work decomposition.
 //
 //   dW[o, k'] += sum over positions P of dy[o, P] * sample(k', P)          k' = tap * Cg + c
 //
@@ -49,7 +51,7 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
 
 template <int D, bool DEFORM>
 __global__ void __launch_bounds__(kWgThreads, 1)
-tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
+tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                 const uint8_t* __restrict__ dpk, float* __restrict__ dw, const int MT, const int MB,
                 const int NB, const int NW, const long long PC, const int chunks_per_split) {
     extern __shared__ uint8_t smem_raw[];
@@ -221,11 +223,11 @@ inline WgDims wg_dims(const Geom& g) {
 }
 
 template <int D, bool DEFORM>
-int launch_tc_wgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk, float* dw,
+int launch_tc_wgrad_direct(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk, float* dw,
                     cudaStream_t st) {
     const WgDims d = wg_dims(g);
     const int smem = WgSmem::kTotal + 1024;
-    auto kern = tc_wgrad_kernel<D, DEFORM>;
+    auto kern = tc_wgrad_direct_kernel<D, DEFORM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     dim3 grid((unsigned)(g.G * d.MB * d.NB), (unsigned)d.splits);
     kern<<<grid, kWgThreads, smem, st>>>(g, xcl, off, dpk, dw, d.MT, d.MB, d.NB, d.NW, d.PC, d.cps);

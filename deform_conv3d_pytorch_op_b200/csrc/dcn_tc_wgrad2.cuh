@@ -1,0 +1,303 @@
+// Weight gradient on tcgen05 (included by dcn_tc.cu inside its anonymous namespace).
+//
+//   dW[o, k'] += sum over positions P of dy[o, P] * sample(k', P)          k' = tap * Cg + c
+//
+// GEMM view: M = output channels (128-row tiles, up to two per CTA), N = a block of up to 256 k' columns,
+// K = output positions, 64 per pipeline stage.  One CTA owns one (group, o-block, k'-block) and a slice of
+// the position range; partial sums are added to dW with fp32 atomics (dW is tiny and L2-resident).
+//   A operand: dy, bf16, pre-packed by pack_dy into swizzled [128 o][64 P] tiles  -> K-major, bulk-copied
+//   B operand: sampled patch, [64 P rows][64 k' per 128-byte row] sub-tiles        -> MN-major, produced here
+// Warps: 0 MMA issue, 1 dy-tile loader, 2-3 coordinate warps, 4-11 gather warps (dcn_tc_sampler.cuh),
+// 12-15 epilogue.  The k' block of a CTA is fixed, so the (deformable group, tap) key of every chunk column and
+// the slot numbering are computed once.
+#pragma once
+
+constexpr int kWg2Threads = 32 * (2 + kCoordWarps + kGatherWarps + kEpilogueWarps);
+
+struct Wg2Ctl {
+    uint64_t full[kMaxStages], empty[kMaxStages], acc_full, tab_full[kMaxTabs], tab_empty[kMaxTabs];
+    uint32_t tmem_base;
+    int slot_of_chunk[32];
+    int key_of_slot[32];
+    int nslots;
+};
+
+template <int D, bool DEFORM>
+__global__ void __launch_bounds__(kWg2Threads, 1)
+tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
+                const uint8_t* __restrict__ dpk, float* __restrict__ dw, const int MT, const int MB,
+                const int NB, const int NW, const long long PC, const int chunks_per_split, const int n_stages,
+                const int max_slots, const int n_tabs, const int a_tiles) {
+    using Entry = TabEntry<D, DEFORM>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int stage_bytes = a_tiles * kTileBytes + 4 * 8192;          // A tiles | B (4 sub-tiles of 8 KB)
+    Entry* tab = reinterpret_cast<Entry*>(smem + (size_t)n_stages * stage_bytes);        // [n_tabs][max_slots][64]
+    float* ostage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tab) +
+                                             (size_t)n_tabs * max_slots * 64 * sizeof(Entry));   // [3][max_slots][D][64]
+    Wg2Ctl* ctl = reinterpret_cast<Wg2Ctl*>(ostage + (size_t)kOffRing * max_slots * D * 64);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    const int nb = blockIdx.x % NB;                     // k' block
+    const int mb = (blockIdx.x / NB) % MB;              // o block (two 128-row tiles)
+    const int j = blockIdx.x / NB / MB;                 // conv group
+    const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+    const long long c_begin = (long long)blockIdx.y * chunks_per_split;
+    long long c_end = c_begin + chunks_per_split;
+    if (c_end > PC) c_end = PC;
+    const int n_chunks = (int)(c_end - c_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMaxStages; ++s) {
+            mbar_init(&ctl->full[s], kGatherWarps * 32 + 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        mbar_init(&ctl->acc_full, 1);
+        for (int b = 0; b < kMaxTabs; ++b) {
+            mbar_init(&ctl->tab_full[b], kCoordWarps * 32);
+            mbar_init(&ctl->tab_empty[b], kGatherWarps * 32);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(&ctl->tmem_base, 512);
+        tmem_relinquish();
+    }
+    if (warp == 2) {
+        // keys of the NW/8 chunk columns of this k' block, numbered into slots (once per CTA)
+        int tap_, c_;
+        const int key = chunk_key(g, j, nb * kWgNMax + lane * 8, tap_, c_);
+        const SlotInfo si = make_slots(key, lane, NW / 8);
+        ctl->slot_of_chunk[lane] = lane < NW / 8 ? si.my_slot : 0;
+        for (int sl = 0; sl < si.nslots; ++sl) {
+            const int k = slot_key(si, sl);
+            if (lane == 0) ctl->key_of_slot[sl] = k;
+        }
+        if (lane == 0) ctl->nslots = si.nslots;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+    const uint32_t idesc = make_idesc(128, NW, 0, 1);   // A K-major, B MN-major
+    const int nslots = ctl->nslots;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < n_chunks && ok; ++it) {
+                const uint32_t s = it % n_stages;
+                ok = mbar_wait(&ctl->full[s], (it / n_stages) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_base = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint32_t b_base = a_base + a_tiles * kTileBytes;
+                for (int mt = 0; mt < mtb; ++mt) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
+                        const uint64_t bd = make_desc(b_base + k * 2048, 8192, 1024);
+                        umma_bf16(tmem_base + mt * 256, ad, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(&ctl->empty[s]);
+            }
+            if (ok) umma_commit(&ctl->acc_full);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < n_chunks && ok; ++it) {
+                const uint32_t s = it % n_stages;
+                ok = mbar_wait(&ctl->empty[s], ((it / n_stages) & 1) ^ 1);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)(mtb * kTileBytes));
+                for (int mt = 0; mt < mtb; ++mt) {
+                    const uint8_t* src = dpk + (((size_t)j * MT + mb * 2 + mt) * PC + (c_begin + it)) * kTileBytes;
+                    bulk_g2s(smem + (size_t)s * stage_bytes + mt * kTileBytes, src, kTileBytes, &ctl->full[s]);
+                }
+            }
+        }
+    } else if (warp < 2 + kCoordWarps) {
+        // ------------------------------------------------ coordinate warps: thread = position row of the chunk
+        const int row = threadIdx.x - 64;               // 0..63
+        auto prefetch = [&](int itp) {
+            if (DEFORM && itp < n_chunks) {
+                const long long P = (c_begin + itp) * 64 + row;
+                if (P < g.P) {
+                    const OutPos op = decompose_pos(g, P);
+                    float* dst = ostage + (size_t)(itp % kOffRing) * max_slots * D * 64;
+                    for (int sl = 0; sl < nslots; ++sl) {
+                        const int key = ctl->key_of_slot[sl];
+                        if (key < 0) continue;
+                        const int grp = key / g.kv, tap = key - grp * g.kv;
+                        const float* src = offset_ptr<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op);
+#pragma unroll
+                        for (int a = 0; a < D; ++a) cp_async4(dst + (size_t)(sl * D + a) * 64 + row, src + (size_t)a * g.ov);
+                    }
+                }
+            }
+            cp_async_commit();
+        };
+        prefetch(0);
+        prefetch(1);
+        bool ok = true;
+        for (int it = 0; it < n_chunks && ok; ++it) {
+            prefetch(it + 2);
+            cp_async_wait<2>();
+            const uint32_t tb = it % n_tabs;
+            const long long P = (c_begin + it) * 64 + row;
+            const bool pok = P < g.P;
+            const OutPos op = decompose_pos(g, pok ? P : 0);
+            ok = mbar_wait(&ctl->tab_empty[tb], ((it / n_tabs) & 1) ^ 1);
+            if (!ok) break;
+            const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 64;
+            for (int sl = 0; sl < nslots; ++sl) {
+                const int key = ctl->key_of_slot[sl];
+                float offv[D];
+#pragma unroll
+                for (int a = 0; a < D; ++a) offv[a] = (DEFORM && key >= 0 && pok) ? src[(size_t)(sl * D + a) * 64 + row] : 0.f;
+                fill_entry_from<D, DEFORM>(g, offv, op, pok, key, tab + ((size_t)tb * max_slots + sl) * 64 + row);
+            }
+            mbar_arrive(&ctl->tab_full[tb]);
+        }
+        cp_async_wait<0>();
+    } else if (warp < 2 + kCoordWarps + kGatherWarps) {
+        // ------------------------------------------------ gather warps
+        const int gtid = threadIdx.x - 32 * (2 + kCoordWarps);   // 0..255
+        const int cj = gtid % 32;                   // chunk column (8 channels) inside the k' block
+        const int row0 = gtid / 32;                 // rows row0 + 8*i, i = 0..7
+        constexpr int NQ = DEFORM ? (1 << D) : 1;
+        constexpr int RPP = (D == 2 || !DEFORM) ? 2 : 1;          // rows per pass
+        constexpr int PPS = 8 / RPP;                               // passes per stage
+        const bool col_ok = cj * 8 < NW;
+        int tap_, cch;
+        chunk_key(g, j, nb * kWgNMax + cj * 8, tap_, cch);
+        const int sl = ctl->slot_of_chunk[cj];
+        const uint32_t sub_off = (uint32_t)(cj / 8) * 8192u + (uint32_t)(a_tiles * kTileBytes);
+        struct Pass {
+            uint4 q[RPP][NQ];
+            float w[RPP][NQ];
+            int it, h;
+        };
+        int cit = 0, ch = 0;
+        bool failed = false;
+        auto issue = [&](Pass& p) -> bool {
+            if (cit >= n_chunks || failed) return false;
+            const uint32_t tb = cit % n_tabs;
+            if (ch == 0) {
+                if (!mbar_wait(&ctl->tab_full[tb], (cit / n_tabs) & 1)) { failed = true; return false; }
+            }
+            const Entry* trow = tab + ((size_t)tb * max_slots + sl) * 64;
+#pragma unroll
+            for (int r = 0; r < RPP; ++r) {
+                const int row = row0 + 8 * (ch * RPP + r);
+                const long long P = (c_begin + cit) * 64 + row;
+                uint32_t n = 0, opos = 0;
+                if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
+                if (col_ok) {
+                    gather_issue_w<D, DEFORM>(trow + row, xcl + (size_t)n * g.iv * g.C + cch, g.C, p.q[r], p.w[r]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < NQ; ++e) { p.q[r][e] = make_uint4(0, 0, 0, 0); p.w[r][e] = 0.f; }
+                }
+            }
+            p.it = cit;
+            p.h = ch;
+            if (ch == PPS - 1) mbar_arrive(&ctl->tab_empty[tb]);
+            if (++ch == PPS) { ch = 0; ++cit; }
+            return true;
+        };
+        auto finish = [&](Pass& p) -> bool {
+            const uint32_t s = p.it % n_stages;
+            if (p.h == 0) {
+                if (!mbar_wait(&ctl->empty[s], ((p.it / n_stages) & 1) ^ 1)) { failed = true; return false; }
+            }
+            if (col_ok) {
+                const uint32_t b_base = smem_u32(smem + (size_t)s * stage_bytes) + sub_off;
+#pragma unroll
+                for (int r = 0; r < RPP; ++r) {
+                    const uint4 v = gather_finish_w<D, DEFORM>(p.q[r], p.w[r]);
+                    st_shared_v4(b_base + swz_offset(row0 + 8 * (p.h * RPP + r), cj % 8), v.x, v.y, v.z, v.w);
+                }
+            }
+            if (p.h == PPS - 1) {
+                fence_proxy_async_smem();
+                mbar_arrive(&ctl->full[s]);
+            }
+            return true;
+        };
+        Pass pa, pb;
+        bool ha = issue(pa);
+        while (ha) {
+            const bool hb = issue(pb);
+            if (!finish(pa)) break;
+            if (!hb) break;
+            ha = issue(pa);
+            if (!finish(pb)) break;
+        }
+    } else {
+        const int q = warp & 3;
+        if (n_chunks > 0 && mbar_wait(&ctl->acc_full, 0)) {
+            tc_fence_after();
+            for (int mt = 0; mt < mtb; ++mt) {
+                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
+                const bool o_ok = ol < g.Og;
+                float* dwo = dw + (size_t)(j * g.Og + (o_ok ? ol : 0)) * g.Cg * g.kv;
+                for (int cc = 0; cc < NW / 32; ++cc) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 32, v);
+                    tmem_ld_wait();
+                    if (!o_ok) continue;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int kq = nb * kWgNMax + cc * 32 + i;
+                        if (kq < g.kv * g.Cg) {
+                            uint32_t tp, cq;
+                            g.d_Cg.divmod((uint32_t)kq, tp, cq);
+                            atomicAdd(dwo + (size_t)cq * g.kv + tp, __uint_as_float(v[i]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Largest number of distinct keys among the chunk columns of any 256-wide k' block.
+inline int max_slots_per_block(const Geom& g) { return max_slots_per_chunk(g, 32); }
+
+template <int D, bool DEFORM>
+int launch_tc_wgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk, float* dw,
+                    cudaStream_t st) {
+    const WgDims d = wg_dims(g);
+    const int a_tiles = d.MT >= 2 ? 2 : 1;
+    const int stage_bytes = a_tiles * kTileBytes + 4 * 8192;
+    const int max_slots = max_slots_per_block(g);
+    const size_t tab_one = (size_t)max_slots * 64 * sizeof(TabEntry<D, DEFORM>);
+    const size_t ost_bytes = (size_t)kOffRing * max_slots * D * 64 * sizeof(float);
+    int n_tabs = kMaxTabs;
+    size_t fixed = n_tabs * tab_one + ost_bytes + sizeof(Wg2Ctl) + 1024;
+    if ((kSmemLimit - (long long)fixed) / stage_bytes < 3) {
+        n_tabs = 2;
+        fixed = n_tabs * tab_one + ost_bytes + sizeof(Wg2Ctl) + 1024;
+    }
+    int stages = (int)((kSmemLimit - (long long)fixed) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2 || max_slots > 32) return launch_tc_wgrad_direct<D, DEFORM>(g, xcl, off, dpk, dw, st);
+    const int smem = (int)(fixed + (size_t)stages * stage_bytes);
+    auto kern = tc_wgrad_kernel<D, DEFORM>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
+    dim3 grid((unsigned)(g.G * d.MB * d.NB), (unsigned)d.splits);
+    kern<<<grid, kWg2Threads, smem, st>>>(g, xcl, off, dpk, dw, d.MT, d.MB, d.NB, d.NW, d.PC, d.cps, stages, max_slots,
+                                          n_tabs, a_tiles);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
