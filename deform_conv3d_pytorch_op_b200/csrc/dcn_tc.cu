@@ -176,6 +176,7 @@ int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cuda
 #include "dcn_tc_wgrad.cuh"
 #include "dcn_tc_wgrad2.cuh"
 #include "dcn_tc_dgrad.cuh"
+#include "dcn_tc_dgrad2.cuh"
 
 struct BwdWeightWorkspace {
     size_t xcl_off, dpk_off, total;

@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait_hint(bar, parity, 20000u)) {
+    while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > kWaitCycles) {
             atomicOr(&g_tc_status, 1u);
             return false;

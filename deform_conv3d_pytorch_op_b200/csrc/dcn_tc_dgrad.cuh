@@ -1,4 +1,7 @@
-// Input and offset gradients on tcgen05 (included by dcn_tc.cu inside its anonymous namespace).
+// Input and offset gradients on tcgen05, row-wise epilogue variant (included by dcn_tc.cu inside its anonymous
+// namespace): every epilogue thread keeps its output position for the scatter as well.  Fallback of
+// dcn_tc_dgrad2.cuh for channel-group sizes that variant does not take; also defines the packers, the
+// work decomposition and the GEMM description shared by both.
 //
 //   col[P, k'] = sum over o of dy[o, P] * W[o, k']                    k' = tap * Cg + c
 // is produced tile by tile in tensor memory and consumed there: the epilogue threads (one per output
@@ -75,7 +78,7 @@ add_from_channels_last(const float* __restrict__ dxcl, float* __restrict__ dx, i
 
 template <int D, bool DEFORM>
 __global__ void __launch_bounds__(kDgThreads, 1)
-tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
+tc_dgrad_rowwise_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                 const uint8_t* __restrict__ dpk, const uint8_t* __restrict__ wpk, float* __restrict__ dxcl,
                 float* __restrict__ doff, const int MT, const int NB, const int NW, const int OC,
                 const long long PC2, const long long PT) {
@@ -309,11 +312,11 @@ inline DgDims dg_dims(const Geom& g) {
 }
 
 template <int D, bool DEFORM>
-int launch_tc_dgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk,
+int launch_tc_dgrad_rowwise(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk,
                     const uint8_t* wpk, float* dxcl, float* doff, cudaStream_t st) {
     const DgDims d = dg_dims(g);
     const int smem = DgSmem::kTotal + 1024;
-    auto kern = tc_dgrad_kernel<D, DEFORM>;
+    auto kern = tc_dgrad_rowwise_kernel<D, DEFORM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     const long long tiles = (long long)g.G * d.PT * d.NB;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());

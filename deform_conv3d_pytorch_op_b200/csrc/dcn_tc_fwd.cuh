@@ -220,8 +220,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         const int chunk = gtid % 8;                 // 16-byte chunk of the 128-byte row
         const int row0 = gtid / 8;                  // rows row0 + 32*i, i = 0..3
         constexpr int NQ = DEFORM ? (1 << D) : 1;
-        constexpr int RPP = (D == 2 || !DEFORM) ? 2 : 1;          // rows per pass
+        constexpr int RPP = 2;                                     // rows per pass
         constexpr int PPS = 4 / RPP;                               // passes per stage
+        // 2-D: the next pass is issued before the current one is finished (16 loads in flight);
+        // 3-D: one pass at a time already has 16 loads in flight, and two would not fit the register file.
+        constexpr bool kOverlap = (D == 2 || !DEFORM);
         struct Pass {
             uint4 q[RPP][NQ];
             float w[RPP][NQ];
@@ -299,14 +302,21 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             }
             return true;
         };
-        Pass pa, pb;
-        bool ha = issue(pa);
-        while (ha) {
-            const bool hb = issue(pb);
-            if (!finish(pa)) break;
-            if (!hb) break;
-            ha = issue(pa);
-            if (!finish(pb)) break;
+        if constexpr (kOverlap) {
+            Pass pa, pb;
+            bool ha = issue(pa);
+            while (ha) {
+                const bool hb = issue(pb);
+                if (!finish(pa)) break;
+                if (!hb) break;
+                ha = issue(pa);
+                if (!finish(pb)) break;
+            }
+        } else {
+            Pass pa;
+            while (issue(pa)) {
+                if (!finish(pa)) break;
+            }
         }
     } else {
         // ------------------------------------------------ epilogue
@@ -409,8 +419,7 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     }
     int stages = (int)((kSmemLimit - (long long)fixed) / kFwdStageBytes);
     if (stages > kMaxStages) stages = kMaxStages;
-    // 3-D sampling (8 corners) is bound by loads in flight per thread, where the direct variant does better.
-    if (stages < 3 || (D == 3 && DEFORM)) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);
+    if (stages < 3) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
     const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
     auto kern = tc_forward_kernel<D, DEFORM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;

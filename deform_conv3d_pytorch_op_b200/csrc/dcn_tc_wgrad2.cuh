@@ -169,8 +169,9 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         const int cj = gtid % 32;                   // chunk column (8 channels) inside the k' block
         const int row0 = gtid / 32;                 // rows row0 + 8*i, i = 0..7
         constexpr int NQ = DEFORM ? (1 << D) : 1;
-        constexpr int RPP = (D == 2 || !DEFORM) ? 2 : 1;          // rows per pass
+        constexpr int RPP = 2;                                     // rows per pass
         constexpr int PPS = 8 / RPP;                               // passes per stage
+        constexpr bool kOverlap = (D == 2 || !DEFORM);             // see dcn_tc_fwd.cuh
         const bool col_ok = cj * 8 < NW;
         int tap_, cch;
         chunk_key(g, j, nb * kWgNMax + cj * 8, tap_, cch);
@@ -228,14 +229,21 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             }
             return true;
         };
-        Pass pa, pb;
-        bool ha = issue(pa);
-        while (ha) {
-            const bool hb = issue(pb);
-            if (!finish(pa)) break;
-            if (!hb) break;
-            ha = issue(pa);
-            if (!finish(pb)) break;
+        if constexpr (kOverlap) {
+            Pass pa, pb;
+            bool ha = issue(pa);
+            while (ha) {
+                const bool hb = issue(pb);
+                if (!finish(pa)) break;
+                if (!hb) break;
+                ha = issue(pa);
+                if (!finish(pb)) break;
+            }
+        } else {
+            Pass pa;
+            while (issue(pa)) {
+                if (!finish(pa)) break;
+            }
         }
     } else {
         const int q = warp & 3;
