@@ -13,11 +13,11 @@
 //            accumulated per lane and, when the key ends, reduced across the lanes of the key with shuffles;
 //   flush    (thread = position again) the 2^D dot products become the D offset-gradient components through
 //            the interpolation-weight derivatives and are added to dOffset, coalesced along positions.
-// Taken when key boundaries fall on multiples of 32 channels (Cg and cpg multiples of 32); the code also handles
-// 16-channel keys (two keys per chunk), which the dispatcher currently leaves to the row-wise variant.
+// Taken when key boundaries fall on multiples of 32 channels (Cg and cpg multiples of 32): every 32-column chunk then
+// belongs to exactly one key.  Other channel-group sizes use the row-wise variant.
 #pragma once
 
-constexpr int kDg2Stages = 3;
+constexpr int kDg2Stages = 2;
 
 template <int D, bool DEFORM>
 struct alignas(16) DgEntry {
@@ -28,26 +28,29 @@ struct alignas(16) DgEntry {
     int pad[2];
 };
 
-template <int D, bool DEFORM>
+template <int D, bool DEFORM, int EW>
 struct Dg2Smem {
     static constexpr int kStageBytes = 3 * kTileBytes;                         // A 16 KB | B 32 KB
     static constexpr int kStagesBytes = kDg2Stages * kStageBytes;
     static constexpr int kColFloats = 32 * 36;                                 // per warp: 32 rows x (32 + 4 pad)
-    static constexpr int kEntryBytes = 2 * 32 * (int)sizeof(DgEntry<D, DEFORM>);   // per warp: 2 slots x 32 rows
-    static constexpr int kWarpBytes = kColFloats * 4 + kEntryBytes;
-    static constexpr int kBarOffset = kStagesBytes + kDgEpiWarps * kWarpBytes;
+    static constexpr int kTotFloats = 32 * 12;                                 // per warp: 32 rows x (2^D + 1, padded)
+    static constexpr int kEntryBytes = 32 * (int)sizeof(DgEntry<D, DEFORM>);   // per warp: 32 rows
+    static constexpr int kWarpBytes = (kColFloats + kTotFloats) * 4 + kEntryBytes;
+    static constexpr int kBarOffset = kStagesBytes + EW * kWarpBytes;
     static constexpr int kTotal = kBarOffset + (2 * kDg2Stages + 4) * 8 + 16;
 };
 
-template <int D, bool DEFORM>
-__global__ void __launch_bounds__(kDgThreads, 1)
+// EW epilogue warps: 8 (each 128 columns of the tile) or 16 (each 64 columns).
+template <int D, bool DEFORM, int EW>
+__global__ void __launch_bounds__(32 * (2 + EW), 1)
 tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                 const uint8_t* __restrict__ dpk, const uint8_t* __restrict__ wpk, float* __restrict__ dxcl,
                 float* __restrict__ doff, const int MT, const int NB, const int NW, const int OC,
-                const long long PC2, const long long PT, const int u) {
-    using SM = Dg2Smem<D, DEFORM>;
+                const long long PC2, const long long PT) {
+    using SM = Dg2Smem<D, DEFORM, EW>;
     using Entry = DgEntry<D, DEFORM>;
     constexpr int NC = 1 << D;
+    constexpr int kColsPerWarp = 256 / (EW / 4);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::kBarOffset);
@@ -65,7 +68,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kDgEpiWarps * 32);
+            mbar_init(&acc_empty[b], EW * 32);
         }
         fence_barrier_init();
     }
@@ -134,16 +137,15 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         }
     } else {
         // ------------------------------------------------ epilogue
-        const int ew = warp - 2;                        // 0..7
+        const int ew = warp - 2;
         const int q = warp & 3;                         // tensor-memory lane quarter
-        const int half = ew / 4;                        // which 128-column half of the tile
+        const int part = ew / 4;                        // which column range of the tile
         float* colS = reinterpret_cast<float*>(smem + SM::kStagesBytes + (size_t)ew * SM::kWarpBytes);   // [32][36]
-        Entry* ent = reinterpret_cast<Entry*>(colS + SM::kColFloats);                                     // [2][32]
+        float* tot = colS + SM::kColFloats;                                                               // [32][12]
+        Entry* ent = reinterpret_cast<Entry*>(tot + SM::kTotFloats);                                      // [32]
         const int kq_total = g.kv * g.Cg;
-        const int ns = 32 / u;                          // keys (slots) per 32-column chunk: 1 or 2
-        // phase-B coordinates of this lane
-        const int r4 = lane >> 3, cq = lane & 7;
-        const int my_slot = (cq * 4) / u;
+        const int r4 = lane >> 3, cq = lane & 7;        // phase-B coordinates of this lane
+        const bool want_x = DEFORM && doff != nullptr;
         uint32_t tl = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
@@ -160,128 +162,79 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             if (!ok) break;
             tc_fence_after();
 
-            // per-slot state: phase A keeps the located point, phase B the running dot products
-            int key[2] = {-1, -1};
-            Pt<float, D> pts[2];
-            pts[0].valid = pts[1].valid = false;
-            float T[8][NC];                // [row iteration][corner] for this lane's slot
-            float S[8];
-#pragma unroll
-            for (int rr = 0; rr < 8; ++rr) {
-                S[rr] = 0.f;
-#pragma unroll
-                for (int e = 0; e < NC; ++e) T[rr][e] = 0.f;
-            }
+            int key = -1;
+            Pt<float, D> pts;
+            pts.valid = false;
 
-            // reduce this lane's accumulators over the lanes of its key and hand the totals of slot `sl` to the
-            // position-owning threads, which turn them into offset-gradient components
-            auto flush = [&](int sl) {
-                if (!DEFORM || doff == nullptr) return;
+            // position-owning thread: turn the accumulated dot products of the finished key into offset gradients
+            auto flush = [&]() {
+                if (!DEFORM || doff == nullptr || key < 0) return;
                 __syncwarp();
+                if (p_ok) {
+                    float tv[NC];
 #pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    float vals[NC + 1];
-#pragma unroll
-                    for (int e = 0; e < NC; ++e) vals[e] = T[rr][e];
-                    vals[NC] = S[rr];
-#pragma unroll
-                    for (int e = 0; e <= NC; ++e) {
-                        float v = vals[e];
-                        v += __shfl_xor_sync(0xffffffffu, v, 1);
-                        v += __shfl_xor_sync(0xffffffffu, v, 2);
-                        if (u == 32) v += __shfl_xor_sync(0xffffffffu, v, 4);
-                        vals[e] = v;
-                    }
-                    if (my_slot == sl && (cq * 4) % u == 0) {
-#pragma unroll
-                        for (int e = 0; e <= NC; ++e) colS[(rr * 4 + r4) * 36 + e] = vals[e];
-                    }
-                    if (my_slot == sl) {
-                        S[rr] = 0.f;
-#pragma unroll
-                        for (int e = 0; e < NC; ++e) T[rr][e] = 0.f;
-                    }
-                }
-                __syncwarp();
-                if (p_ok && key[sl] >= 0) {
-                    float tot[NC];
-#pragma unroll
-                    for (int e = 0; e < NC; ++e) tot[e] = colS[lane * 36 + e];
-                    const float stot = colS[lane * 36 + NC];
+                    for (int e = 0; e < NC; ++e) tv[e] = tot[lane * 12 + e];
                     float gr[D];
-                    if (pts[sl].valid) {
-                        interp_grad<float, D>(pts[sl], tot, gr);
+                    if (pts.valid) {
+                        interp_grad<float, D>(pts, tv, gr);
                     } else {
+                        const float stot = tot[lane * 12 + NC];
 #pragma unroll
-                        for (int a = 0; a < D; ++a) gr[a] = (D == 3 && g.oob) ? oob_term<float>(g, pts[sl].p[a], stot) : 0.f;
+                        for (int a = 0; a < D; ++a) gr[a] = (D == 3 && g.oob) ? oob_term<float>(g, pts.p[a], stot) : 0.f;
                     }
-                    float* dst = doff + ((size_t)op.n * g.dg * g.kv * D + (size_t)key[sl] * D) * g.ov + op.opos;
+                    float* dst = doff + ((size_t)op.n * g.dg * g.kv * D + (size_t)key * D) * g.ov + op.opos;
 #pragma unroll
                     for (int a = 0; a < D; ++a)
                         if (gr[a] != 0.f) atomicAdd(dst + (size_t)a * g.ov, gr[a]);
                 }
-                __syncwarp();
             };
 
-            for (int cc = 0; cc < 4; ++cc) {
-                const int col0 = half * 128 + cc * 32;
+            for (int cc = 0; cc < kColsPerWarp / 32; ++cc) {
+                const int col0 = part * kColsPerWarp + cc * 32;
                 if (col0 >= NW) break;
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 256 + col0, v);
                 tmem_ld_wait();
                 const int kq0 = nb * 256 + col0;
                 if (kq0 >= kq_total) break;
-                // keys of the chunk's slots (uniform across the warp)
-                int nkey[2], ch0[2];
+                uint32_t tap, cl;
+                g.d_Cg.divmod((uint32_t)kq0, tap, cl);
+                const int ch0 = j * g.Cg + (int)cl;                 // first channel of the chunk
+                const int nkey = DEFORM ? (int)g.d_cpg.div((uint32_t)ch0) * g.kv + (int)tap : (int)tap;
+                if (nkey != key) {
+                    flush();
+                    key = nkey;
+                    // phase A: locate the point of the new key and publish it; reset the key's accumulators
+                    Entry e;
+                    e.n = op.n; e.valid = 0; e.pad[0] = e.pad[1] = 0;
 #pragma unroll
-                for (int sl = 0; sl < 2; ++sl) {
-                    nkey[sl] = -1; ch0[sl] = 0;
-                    const int kq = kq0 + sl * u;
-                    if (sl < ns && kq < kq_total) {
-                        uint32_t tap, cl;
-                        g.d_Cg.divmod((uint32_t)kq, tap, cl);
-                        ch0[sl] = j * g.Cg + (int)cl;
-                        nkey[sl] = DEFORM ? (int)g.d_cpg.div((uint32_t)ch0[sl]) * g.kv + (int)tap : (int)tap;
-                    }
-                }
-                // a slot whose key changes first hands over the finished key
-#pragma unroll
-                for (int sl = 0; sl < 2; ++sl) {
-                    if (sl < ns && nkey[sl] != key[sl]) {
-                        if (key[sl] >= 0) flush(sl);
-                        key[sl] = nkey[sl];
-                        // phase A: locate and publish
-                        Entry e;
-                        e.n = op.n; e.valid = 0; e.pad[0] = e.pad[1] = 0;
-#pragma unroll
-                        for (int i = 0; i < NC; ++i) { e.idx[i] = 0; e.cw[i] = 0.f; }
-                        pts[sl].valid = false;
-                        if (p_ok && nkey[sl] >= 0) {
-                            if (DEFORM) {
-                                const int grp = nkey[sl] / g.kv, tap = nkey[sl] - grp * g.kv;
-                                locate<float, D>(g, off_n, grp, tap, op, pts[sl]);
-                                if (pts[sl].valid) {
-                                    corner_indices<float, D>(g, pts[sl], e.idx);
-                                    corner_weights<float, D>(pts[sl], e.cw);
-                                    e.valid = 1;
-                                }
-                            } else {
-                                int pidx;
-                                if (locate_plain<D>(g, nkey[sl], op, pidx)) {
-                                    e.valid = 1;
-                                    e.idx[0] = pidx;
-                                    e.cw[0] = 1.f;
-                                }
+                    for (int i = 0; i < NC; ++i) { e.idx[i] = 0; e.cw[i] = 0.f; }
+                    pts.valid = false;
+                    if (p_ok) {
+                        if (DEFORM) {
+                            const int grp = nkey / g.kv, tp = nkey - grp * g.kv;
+                            locate<float, D>(g, off_n, grp, tp, op, pts);
+                            if (pts.valid) {
+                                corner_indices<float, D>(g, pts, e.idx);
+                                corner_weights<float, D>(pts, e.cw);
+                                e.valid = 1;
+                            }
+                        } else {
+                            int pidx;
+                            if (locate_plain<D>(g, nkey, op, pidx)) {
+                                e.valid = 1;
+                                e.idx[0] = pidx;
+                                e.cw[0] = 1.f;
                             }
                         }
-                        __syncwarp();
-                        {
-                            const int4* src = reinterpret_cast<const int4*>(&e);
-                            int4* dst = reinterpret_cast<int4*>(ent + sl * 32 + lane);
-#pragma unroll
-                            for (int i = 0; i < (int)(sizeof(Entry) / 16); ++i) dst[i] = src[i];
-                        }
                     }
+                    __syncwarp();
+                    const int4* src = reinterpret_cast<const int4*>(&e);
+                    int4* dst = reinterpret_cast<int4*>(ent + lane);
+#pragma unroll
+                    for (int i = 0; i < (int)(sizeof(Entry) / 16); ++i) dst[i] = src[i];
+#pragma unroll
+                    for (int i = 0; i < 3; ++i) reinterpret_cast<float4*>(tot + lane * 12)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
                 // stage the 32 columns of this thread's position
                 __syncwarp();
@@ -290,24 +243,22 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     *reinterpret_cast<uint4*>(colS + lane * 36 + 4 * i) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 __syncwarp();
                 // phase B: the entry and the input values of row iteration rr+1 are fetched while rr is consumed
-                const int cbase = ch0[my_slot] + (cq * 4) % u;          // first of this lane's 4 channels
-                const bool lane_ok = nkey[my_slot] >= 0;
+                const int cbase = ch0 + cq * 4;                       // first of this lane's 4 channels
                 constexpr int NE = DEFORM ? NC : 1;
                 struct RowData {
                     float4 c4;
                     float cw[NE];
-                    size_t addr[NE];
+                    int idx[NE];
                     uint2 xv[NE];
-                    int valid;
+                    int n, valid;
                 };
-                const bool want_x = DEFORM && doff != nullptr;
                 auto fetch = [&](int rr, RowData& rd) {
                     const int row = rr * 4 + r4;
-                    const Entry* ep = ent + my_slot * 32 + row;
+                    const Entry* ep = ent + row;
                     const int4 hdr = *reinterpret_cast<const int4*>(&ep->n);      // n, valid, pad, pad
                     rd.c4 = *reinterpret_cast<const float4*>(colS + row * 36 + cq * 4);
-                    rd.valid = lane_ok ? hdr.y : 0;
-                    const size_t base = (size_t)hdr.x * g.iv * g.C + cbase;
+                    rd.valid = hdr.y;
+                    rd.n = hdr.x;
 #pragma unroll
                     for (int i = 0; i < (NE + 3) / 4; ++i) {
                         const int4 ti = reinterpret_cast<const int4*>(ep->idx)[i];
@@ -317,33 +268,70 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             if (4 * i + k < NE) {
-                                rd.addr[4 * i + k] = base + (size_t)ii[k] * g.C;
+                                rd.idx[4 * i + k] = ii[k];
                                 rd.cw[4 * i + k] = ww[k];
                             }
                         }
                     }
+                    const __nv_bfloat16* xb = xcl + (size_t)rd.n * g.iv * g.C + cbase;
 #pragma unroll
                     for (int e = 0; e < NE; ++e)
-                        rd.xv[e] = (want_x && rd.valid) ? __ldg(reinterpret_cast<const uint2*>(xcl + rd.addr[e])) : make_uint2(0, 0);
+                        rd.xv[e] = (want_x && rd.valid) ? __ldg(reinterpret_cast<const uint2*>(xb + (size_t)rd.idx[e] * g.C))
+                                                        : make_uint2(0, 0);
                 };
                 auto consume = [&](int rr, const RowData& rd) {
+                    const int row = rr * 4 + r4;
+                    float d[NC];
+#pragma unroll
+                    for (int e = 0; e < NC; ++e) d[e] = 0.f;
+                    float sabs = 0.f;
                     if (rd.valid) {
+                        float* db = dxcl + (size_t)rd.n * g.iv * g.C + cbase;
 #pragma unroll
                         for (int e = 0; e < NE; ++e) {
                             if (want_x) {
-                                float d = T[rr][e];
-                                d = fmaf(rd.c4.x, bf16_lo(rd.xv[e].x), d); d = fmaf(rd.c4.y, bf16_hi(rd.xv[e].x), d);
-                                d = fmaf(rd.c4.z, bf16_lo(rd.xv[e].y), d); d = fmaf(rd.c4.w, bf16_hi(rd.xv[e].y), d);
-                                T[rr][e] = d;
+                                float a = fmaf(rd.c4.x, bf16_lo(rd.xv[e].x), 0.f);
+                                a = fmaf(rd.c4.y, bf16_hi(rd.xv[e].x), a);
+                                a = fmaf(rd.c4.z, bf16_lo(rd.xv[e].y), a);
+                                d[e] = fmaf(rd.c4.w, bf16_hi(rd.xv[e].y), a);
                             }
                             if (dxcl != nullptr) {
                                 const float wv = rd.cw[e];
-                                atomicAdd(reinterpret_cast<float4*>(dxcl + rd.addr[e]),
+                                atomicAdd(reinterpret_cast<float4*>(db + (size_t)rd.idx[e] * g.C),
                                           make_float4(wv * rd.c4.x, wv * rd.c4.y, wv * rd.c4.z, wv * rd.c4.w));
                             }
                         }
-                    } else if (DEFORM && D == 3 && g.oob && lane_ok) {
-                        S[rr] += fabsf(rd.c4.x) + fabsf(rd.c4.y) + fabsf(rd.c4.z) + fabsf(rd.c4.w);
+                    } else if (DEFORM && D == 3 && g.oob) {
+                        sabs = fabsf(rd.c4.x) + fabsf(rd.c4.y) + fabsf(rd.c4.z) + fabsf(rd.c4.w);
+                    }
+                    if (want_x) {
+                        // transposing butterfly over the 8 lanes of the row: lane cq ends with the total of one corner
+                        int width = NC;
+#pragma unroll
+                        for (int bit = 4; bit >= 1; bit >>= 1) {
+                            if (width > 1) {
+                                const int hw = width / 2;
+#pragma unroll
+                                for (int i = 0; i < NC / 2; ++i) {
+                                    if (i < hw) {
+                                        const float keep = (cq & bit) ? d[hw + i] : d[i];
+                                        const float send = (cq & bit) ? d[i] : d[hw + i];
+                                        d[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+                                    }
+                                }
+                                width = hw;
+                            } else {
+                                d[0] += __shfl_xor_sync(0xffffffffu, d[0], bit);
+                            }
+                        }
+                        const int corner = (NC == 8) ? cq : (cq >> 1);
+                        if (NC == 8 || (cq & 1) == 0) tot[row * 12 + corner] += d[0];
+                        if (D == 3 && g.oob) {
+                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 4);
+                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 2);
+                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 1);
+                            if (cq == 0) tot[row * 12 + NC] += sabs;
+                        }
                     }
                 };
                 RowData ra, rb;
@@ -356,9 +344,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     consume(rr + 1, rb);
                 }
             }
-#pragma unroll
-            for (int sl = 0; sl < 2; ++sl)
-                if (sl < ns && key[sl] >= 0) flush(sl);
+            flush();
             tc_fence_before();
             mbar_arrive(&acc_empty[b]);
         }
@@ -389,11 +375,12 @@ int launch_tc_dgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, c
     const int u = dgrad_key_unit(g, DEFORM ? 1 : 0);
     if (u == 0) return launch_tc_dgrad_rowwise<D, DEFORM>(g, xcl, off, dpk, wpk, dxcl, doff, st);
     const DgDims d = dg_dims(g);
-    const int smem = Dg2Smem<D, DEFORM>::kTotal + 1024;
-    auto kern = tc_dgrad_kernel<D, DEFORM>;
+    constexpr int EW = (D == 2 || !DEFORM) ? 16 : 8;        // the 3-D epilogue needs the larger register budget
+    const int smem = Dg2Smem<D, DEFORM, EW>::kTotal + 1024;
+    auto kern = tc_dgrad_kernel<D, DEFORM, EW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     const long long tiles = (long long)g.G * d.PT * d.NB;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, kDgThreads, smem, st>>>(g, xcl, off, dpk, wpk, dxcl, doff, d.MT, d.NB, d.NW, d.OC, d.PC2, d.PT, u);
+    kern<<<grid, 32 * (2 + EW), smem, st>>>(g, xcl, off, dpk, wpk, dxcl, doff, d.MT, d.NB, d.NW, d.OC, d.PC2, d.PT);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
