@@ -129,13 +129,122 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def run_model(args):
+    """Config 5: one SGD training step of the R3D-18-style network with deformable stages 3-4 on N = 64 clips of
+    3x16x112x112, the batch split over the ranks (strong scaling), parameter gradients all-reduced over NCCL."""
+    import torch.nn.functional as F
+    from deform_conv3d_pytorch_op_b200 import r3d, _lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model and no CPU path; "
+                              "config 5 has no reference arm (operator-level arm: --config 1..4)"}), flush=True)
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU implementation)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    total = args.batch if args.batch > 0 else 64
+    g = torch.Generator().manual_seed(0)
+    labels_all = torch.randint(0, 400, (total,), generator=g)
+    per = total // world
+    gs = torch.Generator().manual_seed(100 + rank)
+    x_h = torch.randn((per, 3, 16, 112, 112), generator=gs).pin_memory()
+    y_h = labels_all[rank * per:(rank + 1) * per].contiguous().pin_memory()
+    torch.manual_seed(0)
+    prec = "auto" if args.precision == "auto" else args.precision
+    model = r3d.R3D18Deform(400, 64, precision=prec).to(dev)
+    use_ddp = world > 1 and not args.no_ddp
+    net = model
+    if use_ddp:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    x_d, y_d = x_h.to(dev), y_h.to(dev)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        r3d.train_step(net, opt, x_d, y_d, world, ddp=use_ddp)
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    a, b = ev(), ev()
+    sync_all()
+    a.record()
+    for _ in range(args.steps):
+        r3d.train_step(net, opt, x_d, y_d, world, ddp=use_ddp)
+    b.record()
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = a.elapsed_time(b) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    _lib.check(_lib.lib().dcn_check_status(_lib.current_stream(dev)), "device status after the timed region")
+
+    # end to end: the shard comes from pinned host memory every step and the loss goes back to the host
+    e2e = None
+    if not args.no_e2e:
+        def e2e_step():
+            xd = x_h.to(dev, non_blocking=True)
+            yd = y_h.to(dev, non_blocking=True)
+            return float(r3d.train_step(net, opt, xd, yd, world, ddp=use_ddp))
+        for _ in range(2):
+            e2e_step()
+        sync_all()
+        n_e2e = max(3, min(args.steps, 10))
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        sync_all()
+        e_ms = a.elapsed_time(b) / n_e2e
+        if world > 1:
+            t = torch.tensor([e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        e2e = {"value": total / (e_ms * 1e-3), "unit": "clips/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": (x_h.numel() * 4 + y_h.numel() * 8) * world, "d2h_bytes_per_step": 4 * world}
+    if rank == 0:
+        n_deform = sum(1 for m_ in model.modules() if isinstance(m_, r3d.DeformUnit))
+        line = {
+            "metric": "r3d18_deform_train_clips_per_s", "value": total / (ms * 1e-3), "unit": "clips/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (deformable layers, fp32 I/O) + tf32/fp32 (cuDNN layers)",
+            "data": "synthetic",
+            "config": {"workload": "cfg5_r3d18_deform_stage3_4", "global_batch": total, "per_gpu_batch": per,
+                       "clip": [3, 16, 112, 112], "classes": 400, "optimizer": "SGD momentum 0.9",
+                       "parallelism": ("ddp x%d" % world) if use_ddp else ("bucketed all-reduce x%d" % world if world > 1 else "single GPU"),
+                       "l2": "activations of one step exceed the 126 MB L2"},
+            "roofline": None, "cpu_baseline": None, "e2e": e2e, "clocks": clocks,
+            # 8 deformable layers x (3 + 5 + 3) library launches per step (the other layers are cuDNN / torch)
+            "gpu_launches": n_deform * 11 * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--no-ddp", action="store_true", help="config 5: bucketed all-reduce after backward instead of DDP")
     ap.add_argument("--precision", default="auto", choices=["auto", "exact", "bf16"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (0: the configuration's)")
     ap.add_argument("--ref-samples", type=int, default=8, help="samples per step of the --impl reference arm")
@@ -143,6 +252,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
+
+    if args.config == 5:
+        run_model(args)
+        return
 
     from deform_conv3d_pytorch_op_b200 import workloads
     wl = workloads.CONFIGS[args.config]
