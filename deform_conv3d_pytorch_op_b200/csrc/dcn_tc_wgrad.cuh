@@ -213,7 +213,7 @@ inline WgDims wg_dims(const Geom& g) {
     d.NW = kq >= kWgNMax ? kWgNMax : ((kq + 63) / 64) * 64;
     d.PC = 2 * ((g.P + 127) / 128);     // 64-position chunks, even count (shared tile layout with dgrad)
     const long long items = (long long)g.G * d.MB * d.NB;
-    long long splits = (sm_count() + items - 1) / items;
+    long long splits = sm_count() / items;      // floor: the whole grid must fit in one wave (one CTA per SM)
     if (splits > d.PC) splits = d.PC;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;
