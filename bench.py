@@ -425,6 +425,11 @@ def main():
             ach = pass_bytes / (pass_ms[dom] * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": ach / peaks["hbm_gbs"]}
+        # second reading of the target: three gather / scatter passes (forward gather, weight-gradient gather,
+        # input-gradient scatter) of 2^D fp32 corners per sample at HBM bandwidth
+        t_gs = 3.0 * wl.bytes_gather_scatter() / (peaks["hbm_gbs"] * 1e9)
+        roof.update({"gather_scatter": {"bytes_per_pass": wl.bytes_gather_scatter(), "passes": 3,
+                                        "t_roof_ms": t_gs * 1e3, "frac": t_gs / (ms_per_step * 1e-3)}})
         roof.update({"kernel": dom, "kernel_ms": pass_ms[dom], "traffic": None, "peak_source": peaks["source"],
                      "pass_ms": pass_ms,
                      "whole_step_frac": max(wl.flops() / (peaks["bf16_tflops"] * 1e12),

@@ -33,7 +33,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                   const uint8_t* __restrict__ wpk, const float* __restrict__ bias, float* __restrict__ y,
                   const int KC, const int MT, const int MB, const long long PT, const int n_stages,
-                  const int max_slots, const int n_tabs) {
+                  const int max_slots, const int n_tabs, const int KS, const int cpk) {
+    // Work item t = ((j * MB + mb) * PT + pt) * KS + ks: split ks owns K chunks [ks*cpk, min(KC, (ks+1)*cpk)).
+    // With KS > 1 (few position tiles, long K) the partial sums are added to a zero-filled y with atomics.
     using Entry = TabEntry<D, DEFORM>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -68,7 +70,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    const long long n_tiles = (long long)g.G * MB * PT;
+    const long long n_tiles = (long long)g.G * MB * PT * KS;
     constexpr uint32_t kIdesc = make_idesc(128, kTileN, 0, 0);
 
     if (warp == 0) {
@@ -77,12 +79,15 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             uint32_t it = 0, tl = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
-                const int mb = (int)((t / PT) % MB);
+                const int ks = (int)(t % KS);
+                const long long tt = t / KS;
+                const int mb = (int)((tt / PT) % MB);
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
                 const uint32_t b = tl & 1;
                 ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
                 tc_fence_after();
-                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                for (int kc = kc0; kc < kc1 && ok; ++kc, ++it) {
                     const uint32_t s = it % n_stages;
                     ok = mbar_wait(&ctl->full[s], (it / n_stages) & 1);
                     if (!ok) break;
@@ -94,7 +99,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                         for (int k = 0; k < kTileK / 16; ++k) {
                             const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
                             const uint64_t bd = make_desc(b_base + k * 32, 16, 1024);
-                            umma_bf16(tmem_base + b * 256 + mt * 128, ad, bd, kIdesc, (kc > 0 || k > 0) ? 1u : 0u);
+                            umma_bf16(tmem_base + b * 256 + mt * 128, ad, bd, kIdesc, (kc > kc0 || k > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&ctl->empty[s]);
@@ -108,10 +113,13 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             uint32_t it = 0;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int mb = (int)((t / PT) % MB);
-                const int j = (int)(t / PT / MB);
+                const int ks = (int)(t % KS);
+                const long long tt = t / KS;
+                const int mb = (int)((tt / PT) % MB);
+                const int j = (int)(tt / PT / MB);
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
-                for (int kc = 0; kc < KC && ok; ++kc, ++it) {
+                const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
+                for (int kc = kc0; kc < kc1 && ok; ++kc, ++it) {
                     const uint32_t s = it % n_stages;
                     ok = mbar_wait(&ctl->empty[s], ((it / n_stages) & 1) ^ 1);
                     if (!ok) break;
@@ -130,13 +138,17 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         const int ctid = threadIdx.x - 64;          // 0..63, rows ctid and ctid + 64
         struct Cur {
             long long t;
-            int kc, j;
+            int kc, kc_end, j;
             OutPos op[2];
             bool pok[2];
         };
         auto init_tile = [&](Cur& c) {
-            const long long pt = c.t % PT;
-            c.j = (int)(c.t / PT / MB);
+            const int ks = (int)(c.t % KS);
+            const long long tt = c.t / KS;
+            const long long pt = tt % PT;
+            c.j = (int)(tt / PT / MB);
+            c.kc = ks * cpk;
+            c.kc_end = (c.kc + cpk < KC) ? c.kc + cpk : KC;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const long long P = pt * kTileN + ctid + 64 * i;
@@ -146,8 +158,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         };
         auto advance = [&](Cur& c) {
             if (c.t >= n_tiles) return;
-            if (++c.kc == KC) {
-                c.kc = 0;
+            if (++c.kc == c.kc_end) {
                 c.t += gridDim.x;
                 if (c.t < n_tiles) init_tile(c);
             }
@@ -179,7 +190,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             cp_async_commit();
         };
         Cur cur, pre;
-        cur.t = blockIdx.x; cur.kc = 0;
+        cur.t = blockIdx.x; cur.kc = 0; cur.kc_end = 0;
         if (cur.t < n_tiles) init_tile(cur);
         pre = cur;
         prefetch(pre, 0); advance(pre);
@@ -233,13 +244,17 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         };
         // issue cursor
         long long ct = blockIdx.x;
-        int ckc = 0, ch = 0, cj = 0, cc = 0, csl = 0;
+        int ckc = 0, ckc_end = 0, ch = 0, cj = 0, cc = 0, csl = 0;
         uint32_t cit = 0;
         size_t nbase[4];
         bool failed = false;
         auto init_tile = [&]() {
-            const long long pt = ct % PT;
-            cj = (int)(ct / PT / MB);
+            const int ks = (int)(ct % KS);
+            const long long tt = ct / KS;
+            const long long pt = tt % PT;
+            cj = (int)(tt / PT / MB);
+            ckc = ks * cpk;
+            ckc_end = (ckc + cpk < KC) ? ckc + cpk : KC;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const long long P = pt * kTileN + row0 + 32 * i;
@@ -277,8 +292,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             if (++ch == PPS) {
                 ch = 0;
                 ++cit;
-                if (++ckc == KC) {
-                    ckc = 0;
+                if (++ckc == ckc_end) {
                     ct += gridDim.x;
                     if (ct < n_tiles) init_tile();
                 }
@@ -324,9 +338,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         uint32_t tl = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
-            const long long pt = t % PT;
-            const int mb = (int)((t / PT) % MB);
-            const int j = (int)(t / PT / MB);
+            const int ks = (int)(t % KS);
+            const long long tt = t / KS;
+            const long long pt = tt % PT;
+            const int mb = (int)((tt / PT) % MB);
+            const int j = (int)(tt / PT / MB);
             const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
             const uint32_t b = tl & 1;
             ok = mbar_wait(&ctl->acc_full[b], (tl >> 1) & 1);
@@ -336,7 +352,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;      // output channel within the group
                 const bool o_ok = ol < g.Og;
                 const int o = j * g.Og + ol;
-                const float bv = (bias != nullptr && o_ok) ? __ldg(bias + o) : 0.f;
+                const float bv = (bias != nullptr && o_ok && ks == 0) ? __ldg(bias + o) : 0.f;
 #pragma unroll 1
                 for (int cc = 0; cc < kTileN / 32; ++cc) {
                     uint32_t v[32];
@@ -350,10 +366,12 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                     const bool fast = (opos0 + 32 <= (uint32_t)g.ov) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
                     if (fast) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            *reinterpret_cast<float4*>(dst + 4 * i) =
-                                make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
-                                            __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 val = make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
+                                                           __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
+                            if (KS == 1) *reinterpret_cast<float4*>(dst + 4 * i) = val;
+                            else atomicAdd(reinterpret_cast<float4*>(dst + 4 * i), val);
+                        }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -361,7 +379,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                             if (P < g.P) {
                                 uint32_t n, opos;
                                 g.d_ov.divmod((uint32_t)P, n, opos);
-                                y[((size_t)n * g.O + o) * g.ov + opos] = __uint_as_float(v[i]) + bv;
+                                float* d1 = y + ((size_t)n * g.O + o) * g.ov + opos;
+                                if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
+                                else atomicAdd(d1, __uint_as_float(v[i]) + bv);
                             }
                         }
                     }
@@ -423,8 +443,20 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
     auto kern = tc_forward_kernel<D, DEFORM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
-    const long long tiles = (long long)g.G * d.MB * d.PT;
+    // split the K range when there are fewer tiles than SMs (small batches / late layers of a network)
+    const long long base_tiles = (long long)g.G * d.MB * d.PT;
+    int KS = 1;
+    if (base_tiles * 2 <= sm_count()) {
+        KS = (int)(sm_count() / base_tiles);
+        if (KS > d.KC / 8) KS = d.KC / 8;          // at least 8 chunks per split
+        if (KS < 1) KS = 1;
+    }
+    const int cpk = (d.KC + KS - 1) / KS;
+    KS = (d.KC + cpk - 1) / cpk;
+    if (KS > 1 && cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
+    const long long tiles = base_tiles * KS;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, kFwdThreads, smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs);
+    kern<<<grid, kFwdThreads, smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs,
+                                          KS, cpk);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

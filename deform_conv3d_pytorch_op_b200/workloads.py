@@ -71,6 +71,12 @@ class Workload:
         bwd = 4.0 * ((x + off + w + y) + (x + off + w))
         return fwd, bwd
 
+    def bytes_gather_scatter(self, n: Optional[int] = None) -> float:
+        """Bytes one gathering or scattering pass moves if every sample touches its 2^D corners in fp32:
+        N * C * kv * ov samples x 2^D x 4 B.  Implementation-dependent and mostly cache-resident; informative."""
+        n = self.N if n is None else n
+        return 4.0 * (2 ** self.ndim) * n * self.C * self.kv * self.ov
+
     def bytes_per_pass(self, n: Optional[int] = None):
         """Compulsory fp32 traffic of each pass taken alone (every tensor it reads or writes, once)."""
         n = self.N if n is None else n
