@@ -15,7 +15,7 @@ LIB = os.path.join(CSRC, "libdcn.so")
 SOURCES = ["dcn_api.cu", "dcn_simt.cu", "dcn_tc.cu"]
 HEADERS = ["dcn_common.cuh", "dcn_internal.h", os.path.join("..", "..", "include", "dcn.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + os.environ.get("DCN_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

@@ -15,7 +15,7 @@
 constexpr int kMaxStages = 4;
 constexpr int kCoordWarps = 2;
 constexpr int kGatherWarps = 8;
-constexpr int kFwdThreads = 32 * (2 + kCoordWarps + kGatherWarps + kEpilogueWarps);
+constexpr int fwd_threads(int gw) { return 32 * (2 + kCoordWarps + gw + kEpilogueWarps); }
 constexpr int kFwdStageBytes = 3 * kTileBytes;      // A0 | A1 | B
 constexpr int kSmemLimit = 232448;                   // 227 KB opt-in maximum per CTA
 
@@ -28,8 +28,9 @@ struct FwdCtl {            // lives behind the stages, the tables and the offset
     int slot_of_chunk[kMaxTabs][8];
 };
 
-template <int D, bool DEFORM>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+// GW gather warps: 8 (4 rows per thread and stage) or 16 (2 rows; more warps to hide the gather latency).
+template <int D, bool DEFORM, int GW>
+__global__ void __launch_bounds__(fwd_threads(GW), 1)
 tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                   const uint8_t* __restrict__ wpk, const float* __restrict__ bias, float* __restrict__ y,
                   const int KC, const int MT, const int MB, const long long PT, const int n_stages,
@@ -48,7 +49,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl->full[s], kGatherWarps * 32 + 1);
+            mbar_init(&ctl->full[s], GW * 32 + 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -57,7 +58,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         }
         for (int b = 0; b < kMaxTabs; ++b) {
             mbar_init(&ctl->tab_full[b], kCoordWarps * 32);
-            mbar_init(&ctl->tab_empty[b], kGatherWarps * 32);
+            mbar_init(&ctl->tab_empty[b], GW * 32);
         }
         fence_barrier_init();
     }
@@ -223,16 +224,18 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             ++it;
         }
         cp_async_wait<0>();
-    } else if (warp < 2 + kCoordWarps + kGatherWarps) {
+    } else if (warp < 2 + kCoordWarps + GW) {
         // ------------------------------------------------ gather warps
         // A stage is produced in passes of RPP rows per thread; the loads of the next pass are in flight while
         // the current pass is interpolated and stored, across stage and tile boundaries.
         const int gtid = threadIdx.x - 32 * (2 + kCoordWarps);   // 0..255
         const int chunk = gtid % 8;                 // 16-byte chunk of the 128-byte row
-        const int row0 = gtid / 8;                  // rows row0 + 32*i, i = 0..3
+        const int row0 = gtid / 8;                  // rows row0 + RS*i, i = 0..RT-1
         constexpr int NQ = DEFORM ? (1 << D) : 1;
-        constexpr int RPP = 2;                                     // rows per pass
-        constexpr int PPS = 4 / RPP;                               // passes per stage
+        constexpr int RT = 128 * 8 / (GW * 32);                    // rows per thread and stage: 4 or 2
+        constexpr int RS = GW * 4;                                 // row stride between a thread's rows
+        constexpr int RPP = RT / 2;                                // rows per pass (one row per pass: +31 % time)
+        constexpr int PPS = 2;                                     // passes per stage
         // 2-D: the next pass is issued before the current one is finished (16 loads in flight);
         // 3-D: one pass at a time already has 16 loads in flight, and two would not fit the register file.
         constexpr bool kOverlap = (D == 2 || !DEFORM);
@@ -246,7 +249,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         long long ct = blockIdx.x;
         int ckc = 0, ckc_end = 0, ch = 0, cj = 0, cc = 0, csl = 0;
         uint32_t cit = 0;
-        size_t nbase[4];
+        size_t nbase[RT];
         bool failed = false;
         auto init_tile = [&]() {
             const int ks = (int)(ct % KS);
@@ -256,8 +259,8 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             ckc = ks * cpk;
             ckc_end = (ckc + cpk < KC) ? ckc + cpk : KC;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const long long P = pt * kTileN + row0 + 32 * i;
+            for (int i = 0; i < RT; ++i) {
+                const long long P = pt * kTileN + row0 + RS * i;
                 uint32_t n = 0, opos = 0;
                 if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
                 nbase[i] = (size_t)n * g.iv * g.C;
@@ -282,7 +285,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 for (int hh = 0; hh < PPS; ++hh) {
                     if (hh == ch) {
                         const int i = hh * RPP + r;
-                        gather_issue_w<D, DEFORM>(trow + row0 + 32 * i, xcl + nbase[i] + cc, g.C, p.q[r], p.w[r]);
+                        gather_issue_w<D, DEFORM>(trow + row0 + RS * i, xcl + nbase[i] + cc, g.C, p.q[r], p.w[r]);
                     }
                 }
             }
@@ -308,7 +311,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
 #pragma unroll
             for (int r = 0; r < RPP; ++r) {
                 const uint4 v = gather_finish_w<D, DEFORM>(p.q[r], p.w[r]);
-                st_shared_v4(b_base + swz_offset(row0 + 32 * (p.h * RPP + r), chunk), v.x, v.y, v.z, v.w);
+                st_shared_v4(b_base + swz_offset(row0 + RS * (p.h * RPP + r), chunk), v.x, v.y, v.z, v.w);
             }
             if (p.h == PPS - 1) {
                 fence_proxy_async_smem();
@@ -441,7 +444,8 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 3) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
     const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
-    auto kern = tc_forward_kernel<D, DEFORM>;
+    constexpr int GW = 8;      // 16 gather warps (2 rows each) measured slower: 0.62 ms vs 0.53 ms on the 2-D benchmark shape
+    auto kern = tc_forward_kernel<D, DEFORM, GW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     // split the K range when there are fewer tiles than SMs (small batches / late layers of a network)
     const long long base_tiles = (long long)g.G * d.MB * d.PT;
@@ -456,7 +460,7 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     if (KS > 1 && cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
     const long long tiles = base_tiles * KS;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, kFwdThreads, smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs,
+    kern<<<grid, fwd_threads(GW), smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs,
                                           KS, cpk);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
