@@ -289,7 +289,7 @@ def main():
 
     op = dcn.Op(x, w, wl.stride, wl.pad, wl.dil, wl.cpg, wl.G, precision=args.precision)
     prec = "bf16" if op.p.precision == _lib.PREC_BF16 else "exact"
-    launches_per_step = sum(_lib.lib().dcn_launch_count(ctypes.byref(op.p), ps) for ps in (0, 1, 2))
+    launches_per_step = sum(_lib.lib().dcn_launch_count(ctypes.byref(op.p), ps) for ps in (0, 3))
 
     # L2 hygiene: the working set of configs 2-4 is several times the 126 MB L2; for small ones flush.
     working_set = sum(t.numel() * 4 for t in (x, off, dy)) * 2 + x.numel() * 4
@@ -300,23 +300,27 @@ def main():
     pass_ms = {"forward": 0.0, "backward_data": 0.0, "backward_weight": 0.0}
 
     def step(timed: bool):
+        """The measured step: forward, then all gradients through the fused backward entry point (which takes
+        over the forward's channels-last input copy), then the dW all-reduce when there are several ranks."""
         if flush:
             flush_buf.zero_()
-        e = [ev() for _ in range(4)] if timed else None
-        if timed:
-            e[0].record()
-        y = op.forward(x, off, w, None)
-        if timed:
-            e[1].record()
-        dx, doff = op.backward_data(x, off, w, dy)
-        if timed:
-            e[2].record()
-        dw, _ = op.backward_weight(x, off, dy)
-        if timed:
-            e[3].record()
+        y, fws = op.forward(x, off, w, None, keep_workspace=True)
+        dx, doff, dw, _ = op.backward(x, off, w, dy, True, True, True, False, fws)
         if world > 1:
             dist.all_reduce(dw)
-        return e, (y, dx, doff, dw)
+        return None, (y, dx, doff, dw)
+
+    def breakdown_step():
+        """Same work through the three separate entry points, for the per-pass timings of the roofline object."""
+        e = [ev() for _ in range(4)]
+        e[0].record()
+        op.forward(x, off, w, None)
+        e[1].record()
+        op.backward_data(x, off, w, dy)
+        e[2].record()
+        op.backward_weight(x, off, dy)
+        e[3].record()
+        return e
 
     def sync_all():
         torch.cuda.synchronize()
@@ -342,12 +346,18 @@ def main():
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_begin.elapsed_time(t_end)
+    n_bd = max(3, min(args.steps, 10))
+    for _ in range(2):                      # let the allocator see the separate passes' buffer sizes first
+        breakdown_step()
+    torch.cuda.synchronize()
+    evs = [breakdown_step() for _ in range(n_bd)]
+    torch.cuda.synchronize()
     for e in evs:
         pass_ms["forward"] += e[0].elapsed_time(e[1])
         pass_ms["backward_data"] += e[1].elapsed_time(e[2])
         pass_ms["backward_weight"] += e[2].elapsed_time(e[3])
     for k in pass_ms:
-        pass_ms[k] /= args.steps
+        pass_ms[k] /= n_bd
     if flush:
         # the flush memset sits inside the bracket; measure it alone and take it out
         torch.cuda.synchronize()

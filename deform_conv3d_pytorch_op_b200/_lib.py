@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libdcn.so")
 
 DCN_F32, DCN_F64 = 0, 1
 PREC_EXACT, PREC_BF16 = 0, 1
-PASS_FORWARD, PASS_BACKWARD_DATA, PASS_BACKWARD_WEIGHT = 0, 1, 2
+PASS_FORWARD, PASS_BACKWARD_DATA, PASS_BACKWARD_WEIGHT, PASS_BACKWARD = 0, 1, 2, 3
 
 
 class DcnError(RuntimeError):
@@ -39,7 +39,7 @@ _lib: Optional[ctypes.CDLL] = None
 # every symbol include/dcn.h declares (checked by the CPU test-suite)
 GENERIC_SYMBOLS = [
     "dcn_version", "dcn_status_string", "dcn_output_size", "dcn_validate", "dcn_precision_supported",
-    "dcn_workspace_bytes", "dcn_launch_count", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_debug_points",
+    "dcn_workspace_bytes", "dcn_launch_count", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_backward", "dcn_debug_points",
     "dcn_check_status", "dcn_static_scratch_bytes", "dcn_forward_static_scratch",
 ]
 LEGACY_SYMBOLS = [
@@ -75,6 +75,7 @@ def lib() -> ctypes.CDLL:
         L.dcn_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_backward_data.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_backward_weight.argtypes = [pp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.dcn_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_debug_points.argtypes = [pp, vp, ctypes.c_int32, vp, vp, vp, vp, vp]
         L.dcn_check_status.argtypes = [vp]
         L.dcn_static_scratch_bytes.restype = ctypes.c_size_t

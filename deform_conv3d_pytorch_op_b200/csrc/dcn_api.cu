@@ -121,12 +121,14 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
     Geom g;
     make_geom(p, g);
     if (!dcn::tc_supported(g, p->ndim, p->deformable)) return 0;
+    if (pass == DCN_PASS_BACKWARD) return dcn::tc_backward_workspace_bytes(g);
     return dcn::tc_workspace_bytes(g, p->ndim, pass);
 }
 
 int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
-    if (p->precision == DCN_PREC_EXACT) return 1;
+    if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_BACKWARD ? 2 : 1;
+    if (pass == DCN_PASS_BACKWARD) return 6;      // channels-last copy, dy pack, weight pack, dgrad, dx transpose, wgrad
     Geom g;
     make_geom(p, g);
     return dcn::tc_launch_count(g, p->ndim, pass);
@@ -215,6 +217,43 @@ int dcn_backward_weight(const dcn_problem* p, const void* x, const void* offset,
                                         (const float*)dy, (float*)dweight, ws, ws_bytes, st);
         } else {
             r = dcn::simt_backward_weight(g, p->dtype, p->ndim, p->deformable, x, offset, dy, dweight, st);
+        }
+        if (r != DCN_OK) return r;
+    }
+    if (dbias != nullptr) r = dcn::bias_grad(g, p->dtype, dy, dbias, st);
+    return r;
+}
+
+int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* dy,
+                 const void* x_channels_last, void* dx, void* doffset, void* dweight, void* dbias, void* ws,
+                 size_t ws_bytes, void* stream) {
+    const int v = validate(p);
+    if (v != DCN_OK) return v;
+    if (x == nullptr || weight == nullptr || dy == nullptr || (p->deformable && offset == nullptr)) return DCN_ERR_NULL;
+    const int a = check_ptrs(p, {x, offset, weight, dy, dx, doffset, dweight, dbias});
+    if (a != DCN_OK) return a;
+    Geom g;
+    make_geom(p, g);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int r = DCN_OK;
+    if (dx != nullptr || doffset != nullptr || dweight != nullptr) {
+        if (p->precision == DCN_PREC_BF16) {
+            if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
+            if (!workspace_ok(ws, ws_bytes, dcn::tc_backward_workspace_bytes(g))) return DCN_ERR_WORKSPACE;
+            if (x_channels_last != nullptr && !aligned(x_channels_last, 16)) return DCN_ERR_ALIGN;
+            r = dcn::tc_backward(g, p->ndim, p->deformable, (const float*)x, (const float*)offset, (const float*)weight,
+                                 (const float*)dy, x_channels_last, (float*)dx, (float*)doffset, (float*)dweight, ws,
+                                 ws_bytes, st);
+        } else {
+            const size_t es = p->dtype == DCN_F64 ? 8 : 4;
+            if (dx != nullptr && cudaMemsetAsync(dx, 0, (size_t)g.N * g.C * g.iv * es, st) != cudaSuccess) return DCN_ERR_CUDA;
+            if (dweight != nullptr && cudaMemsetAsync(dweight, 0, (size_t)g.O * g.Cg * g.kv * es, st) != cudaSuccess)
+                return DCN_ERR_CUDA;
+            if (dx != nullptr || doffset != nullptr)
+                r = dcn::simt_backward_data(g, p->dtype, p->ndim, p->deformable, x, offset, weight, dy, dx,
+                                            p->deformable ? doffset : nullptr, st);
+            if (r == DCN_OK && dweight != nullptr)
+                r = dcn::simt_backward_weight(g, p->dtype, p->ndim, p->deformable, x, offset, dy, dweight, st);
         }
         if (r != DCN_OK) return r;
     }

@@ -29,6 +29,10 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
                      const float* dy, float* dx, float* doff, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* dy,
                        float* dw, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t tc_backward_workspace_bytes(const Geom& g);
+int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+                const float* dy, const void* xcl_in, float* dx, float* doff, float* dw, void* ws, size_t ws_bytes,
+                cudaStream_t st);
 int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
                       const float* bias, float* y, cudaStream_t st);
 size_t tc_static_scratch_bytes();

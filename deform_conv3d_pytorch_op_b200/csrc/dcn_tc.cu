@@ -277,7 +277,7 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
     if (r != 0) return r;
     if (dx != nullptr) {
         dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
-        add_from_channels_last<<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
+        from_channels_last<true><<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
         if (cudaGetLastError() != cudaSuccess) return -5;
     }
     return 0;
@@ -299,6 +299,65 @@ int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, cons
                                  : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dw, st);
     return deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dw, st)
                   : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Fused backward: all requested gradients in one call.  The channels-last input copy and the packed dy are
+// built once and shared by the data and weight kernels (or the input copy is taken over from the forward
+// pass), and every output is overwritten, so no caller-side zero fill and no read-modify-write of dx.
+// ---------------------------------------------------------------------------------------------------
+size_t tc_backward_workspace_bytes(const Geom& g) { return bwd_data_workspace(g).total; }
+
+int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+                const float* dy, const void* xcl_in, float* dx, float* doff, float* dw, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+    const BwdDataWorkspace l = bwd_data_workspace(g);
+    if (ws_bytes < l.total) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    const __nv_bfloat16* xcl = static_cast<const __nv_bfloat16*>(xcl_in);
+    uint8_t* dpk = base + l.dpk_off;
+    uint8_t* wpk = base + l.wpk_off;
+    float* dxcl = dx != nullptr ? reinterpret_cast<float*>(base + l.dxcl_off) : nullptr;
+    if (!deform) doff = nullptr;
+    const DgDims d = dg_dims(g);
+    int r = 0;
+    const bool need_x = dw != nullptr || (deform && (dx != nullptr || doff != nullptr));
+    if (xcl == nullptr && need_x) {
+        __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+        r = launch_channels_last(g, x, mine, st);
+        if (r != 0) return r;
+        xcl = mine;
+    }
+    pack_dy<<<dim3((unsigned)d.PC2, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC2);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (dx != nullptr || doff != nullptr) {
+        pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+        if (dxcl != nullptr && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
+        if (doff != nullptr &&
+            cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * ndim * g.ov * sizeof(float), st) != cudaSuccess)
+            return -5;
+        if (ndim == 2) r = deform ? launch_tc_dgrad<2, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
+                                  : launch_tc_dgrad<2, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+        else r = deform ? launch_tc_dgrad<3, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
+                        : launch_tc_dgrad<3, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+        if (r != 0) return r;
+        if (dx != nullptr) {
+            dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+            from_channels_last<false><<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
+            if (cudaGetLastError() != cudaSuccess) return -5;
+        }
+    }
+    if (dw != nullptr) {
+        if (cudaMemsetAsync(dw, 0, (size_t)g.O * g.Cg * g.kv * sizeof(float), st) != cudaSuccess) return -5;
+        // the weight kernel reads dy tiles with the same layout and stride (PC2 == wg_dims().PC)
+        if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dw, st)
+                                  : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dw, st);
+        else r = deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dw, st)
+                        : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
+        if (r != 0) return r;
+    }
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -54,9 +54,10 @@ pack_weight_bwd(const Geom g, const float* __restrict__ w, uint8_t* __restrict__
     }
 }
 
-// dx[n, c, p] += dx_cl[n, p, c]
+// dx[n, c, p] (+)= dx_cl[n, p, c]
+template <bool ACCUMULATE>
 __global__ void __launch_bounds__(256)
-add_from_channels_last(const float* __restrict__ dxcl, float* __restrict__ dx, int C, int iv) {
+from_channels_last(const float* __restrict__ dxcl, float* __restrict__ dx, int C, int iv) {
     __shared__ float tile[32][33];
     const int n = blockIdx.z;
     const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
@@ -72,7 +73,10 @@ add_from_channels_last(const float* __restrict__ dxcl, float* __restrict__ dx, i
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int c = c0 + ty + i * 8, p = p0 + tx;
-        if (c < C && p < iv) out[(size_t)c * iv + p] += tile[tx][ty + i * 8];
+        if (c < C && p < iv) {
+            if (ACCUMULATE) out[(size_t)c * iv + p] += tile[tx][ty + i * 8];
+            else out[(size_t)c * iv + p] = tile[tx][ty + i * 8];
+        }
     }
 }
 

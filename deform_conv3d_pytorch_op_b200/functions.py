@@ -37,19 +37,22 @@ class _ConvOffsetNdFunction(Function):
                     precision=precision)
         ctx.has_bias = bias is not None
         ctx.save_for_backward(inputs, offset, weight)
+        ctx.fwd_ws = None
+        need_bwd = any(t is not None and t.requires_grad for t in (inputs, offset, weight, bias))
+        if need_bwd and torch.is_grad_enabled():
+            y, ctx.fwd_ws = ctx.op.forward(inputs, offset, weight, bias, keep_workspace=True)
+            ctx.x_version = inputs._version
+            return y
         return ctx.op.forward(inputs, offset, weight, bias)
 
     @staticmethod
     def _bwd(ctx, grad_output):
         inputs, offset, weight = ctx.saved_tensors
         need = ctx.needs_input_grad
-        grad_input = grad_offset = grad_weight = grad_bias = None
-        if need[0] or need[1]:
-            grad_input, grad_offset = ctx.op.backward_data(inputs, offset, weight, grad_output, need[0], need[1])
         want_db = ctx.has_bias and need[3]
-        if need[2] or want_db:
-            grad_weight, grad_bias = ctx.op.backward_weight(inputs, offset, grad_output, need[2], want_db)
-        return grad_input, grad_offset, grad_weight, grad_bias
+        xcl = ctx.fwd_ws if (ctx.fwd_ws is not None and inputs._version == ctx.x_version) else None
+        ctx.fwd_ws = None
+        return ctx.op.backward(inputs, offset, weight, grad_output, need[0], need[1], need[2], want_db, xcl)
 
 
 class ConvOffset3dFunction(_ConvOffsetNdFunction):
@@ -88,6 +91,11 @@ class Conv2dFunction(Function):
                     deformable=False, std_size_rule=True, precision=precision)
         ctx.has_bias = bias is not None
         ctx.save_for_backward(inputs, weight)
+        ctx.fwd_ws = None
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (inputs, weight, bias)):
+            y, ctx.fwd_ws = ctx.op.forward(inputs, None, weight, bias, keep_workspace=True)
+            ctx.x_version = inputs._version
+            return y
         return ctx.op.forward(inputs, None, weight, bias)
 
     @staticmethod
@@ -95,12 +103,11 @@ class Conv2dFunction(Function):
     def backward(ctx, grad_output):
         inputs, weight = ctx.saved_tensors
         need = ctx.needs_input_grad
-        grad_input = grad_weight = grad_bias = None
-        if need[0]:
-            grad_input, _ = ctx.op.backward_data(None, None, weight, grad_output, True, False)
         want_db = ctx.has_bias and need[2]
-        if need[1] or want_db:
-            grad_weight, grad_bias = ctx.op.backward_weight(inputs, None, grad_output, need[1], want_db)
+        xcl = ctx.fwd_ws if (ctx.fwd_ws is not None and inputs._version == ctx.x_version) else None
+        ctx.fwd_ws = None
+        grad_input, _, grad_weight, grad_bias = ctx.op.backward(inputs, None, weight, grad_output, need[0], False,
+                                                                need[1], want_db, xcl)
         return grad_input, grad_weight, grad_bias, None, None, None, None, None
 
 

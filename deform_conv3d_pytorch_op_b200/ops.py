@@ -98,7 +98,29 @@ class Op:
             raise DcnError("offset shape %s, expected %s" % (tuple(offset.shape), want))
 
     # -- passes ----------------------------------------------------------------------------------
-    def forward(self, x, offset, weight, bias=None) -> torch.Tensor:
+    def backward(self, x, offset, weight, dy, want_dx=True, want_doffset=True, want_dw=True, want_dbias=False,
+                 x_channels_last: Optional[torch.Tensor] = None):
+        """All gradients through the fused entry point (outputs overwritten; scratch shared between the data
+        and weight kernels).  ``x_channels_last``: the forward workspace kept by :meth:`forward` (bf16 path)."""
+        x = _prep(x, "input")
+        weight = _prep(weight, "weight", x)
+        dy = _prep(dy, "grad_output", x)
+        offset = _prep(offset, "offset", x) if self.deformable else None
+        if not self.deformable:
+            want_doffset = False
+        dx = torch.empty_like(x) if want_dx else None
+        doff = torch.empty_like(offset) if want_doffset else None
+        dw = torch.empty(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
+        db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
+        ws, nb = self._ws(_lib.PASS_BACKWARD)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dcn_backward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
+                                         _lib.ptr(dy), _lib.ptr(x_channels_last), _lib.ptr(dx), _lib.ptr(doff),
+                                         _lib.ptr(dw), _lib.ptr(db), _lib.ptr(ws), nb, _lib.current_stream(x.device))
+        _lib.check(st, "dcn_backward")
+        return dx, doff, dw, db
+
+    def forward(self, x, offset, weight, bias=None, keep_workspace: bool = False):
         x = _prep(x, "input")
         weight = _prep(weight, "weight", x)
         bias = _prep(bias, "bias", x)
@@ -113,6 +135,9 @@ class Op:
             st = _lib.lib().dcn_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
                                         _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), nb, _lib.current_stream(x.device))
         _lib.check(st, "dcn_forward")
+        if keep_workspace:
+            # the channels-last bf16 copy of x sits at the start of the workspace; backward can take it over
+            return y, ws
         return y
 
     def backward_data(self, x, offset, weight, dy, want_dx=True, want_doffset=True

@@ -57,7 +57,7 @@ enum { DCN_F32 = 0, DCN_F64 = 1 };
  * BF16 : fp32 tensors in and out, sampled patches and weights rounded to bf16, tcgen05 MMA with
  *        fp32 accumulation in tensor memory.  Coordinates and interpolation stay fp32. */
 enum { DCN_PREC_EXACT = 0, DCN_PREC_BF16 = 1 };
-enum { DCN_PASS_FORWARD = 0, DCN_PASS_BACKWARD_DATA = 1, DCN_PASS_BACKWARD_WEIGHT = 2 };
+enum { DCN_PASS_FORWARD = 0, DCN_PASS_BACKWARD_DATA = 1, DCN_PASS_BACKWARD_WEIGHT = 2, DCN_PASS_BACKWARD = 3 };
 
 /* One operator instance.  For ndim == 2 only the LAST two slots of each triple are used
  * (slot 0 must hold in=1, k=1, stride=1, pad=0, dil=1). */
@@ -133,6 +133,17 @@ int dcn_backward_data(const dcn_problem* p, const void* x, const void* offset, c
  * (deform_conv3d_function.py:73-74). */
 int dcn_backward_weight(const dcn_problem* p, const void* x, const void* offset, const void* dy, void* dweight,
                         void* dbias, void* workspace, size_t workspace_bytes, void* stream);
+
+/* All gradients in one call (any of dx / doffset / dweight / dbias may be NULL = not wanted).  Unlike the two
+ * calls above, EVERY output is OVERWRITTEN: no zero fill by the caller.  The passes share their scratch
+ * (workspace of dcn_workspace_bytes(p, DCN_PASS_BACKWARD) bytes).  `x_channels_last`, if not NULL, is the
+ * channels-last bf16 copy of x that dcn_forward (precision BF16, same problem, same x) left at the START of
+ * its workspace; passing it saves rebuilding it.  It is ignored by the EXACT precision.
+ * Replaces deform_conv_backward_input_offset_cuda + deform_conv_backward_weight_cuda + the Python-side bias
+ * gradient (deform3d/deform_conv3d_functions/deform_conv3d_function.py:46-77) as one unit. */
+int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* dy,
+                 const void* x_channels_last, void* dx, void* doffset, void* dweight, void* dbias, void* workspace,
+                 size_t workspace_bytes, void* stream);
 
 /* Debug aid for the bit-exactness tests: for sample `n` writes, for every (deformable group, tap,
  * output position), the sampling coordinate (tensor dtype, [dg,kv,ov,ndim]), validity (int32
