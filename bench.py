@@ -158,7 +158,8 @@ def run_model(args):
     torch.manual_seed(0)
     prec = "auto" if args.precision == "auto" else args.precision
     model = r3d.R3D18Deform(400, 64, precision=prec).to(dev)
-    use_ddp = world > 1 and not args.no_ddp
+    use_graph = not args.no_graph
+    use_ddp = world > 1 and not args.no_ddp and not use_graph     # the graphed step all-reduces flat buckets itself
     net = model
     if use_ddp:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
@@ -173,8 +174,15 @@ def run_model(args):
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     warm = max(args.warmup, 3)
+    graphed = r3d.GraphedTrainStep(model, opt, x_d, y_d, world) if use_graph else None
+
+    def one_step(xd=None, yd=None):
+        if graphed is not None:
+            return graphed(xd, yd)
+        return r3d.train_step(net, opt, x_d if xd is None else xd, y_d if yd is None else yd, world, ddp=use_ddp)
+
     for _ in range(warm):
-        r3d.train_step(net, opt, x_d, y_d, world, ddp=use_ddp)
+        one_step()
     sync_all()
     sampler = ClockSampler(local)
     if rank == 0:
@@ -183,7 +191,7 @@ def run_model(args):
     sync_all()
     a.record()
     for _ in range(args.steps):
-        r3d.train_step(net, opt, x_d, y_d, world, ddp=use_ddp)
+        one_step()
     b.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
@@ -198,9 +206,11 @@ def run_model(args):
     e2e = None
     if not args.no_e2e:
         def e2e_step():
+            if graphed is not None:
+                return float(one_step(x_h, y_h))          # pinned host -> static device buffers -> replay
             xd = x_h.to(dev, non_blocking=True)
             yd = y_h.to(dev, non_blocking=True)
-            return float(r3d.train_step(net, opt, xd, yd, world, ddp=use_ddp))
+            return float(one_step(xd, yd))
         for _ in range(2):
             e2e_step()
         sync_all()
@@ -227,6 +237,7 @@ def run_model(args):
             "config": {"workload": "cfg5_r3d18_deform_stage3_4", "global_batch": total, "per_gpu_batch": per,
                        "clip": [3, 16, 112, 112], "classes": 400, "optimizer": "SGD momentum 0.9",
                        "parallelism": ("ddp x%d" % world) if use_ddp else ("bucketed all-reduce x%d" % world if world > 1 else "single GPU"),
+                       "launch": "CUDA graph replay" if use_graph else "eager",
                        "l2": "activations of one step exceed the 126 MB L2"},
             "roofline": None, "cpu_baseline": None, "e2e": e2e, "clocks": clocks,
             # 8 deformable layers x (3 + 5 + 3) library launches per step (the other layers are cuDNN / torch)
@@ -245,6 +256,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--no-ddp", action="store_true", help="config 5: bucketed all-reduce after backward instead of DDP")
+    ap.add_argument("--no-graph", action="store_true", help="config 5: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--precision", default="auto", choices=["auto", "exact", "bf16"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (0: the configuration's)")
     ap.add_argument("--ref-samples", type=int, default=8, help="samples per step of the --impl reference arm")

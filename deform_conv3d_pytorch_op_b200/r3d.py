@@ -133,3 +133,43 @@ def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor
         all_reduce_grads(model.module if hasattr(model, "module") else model, world)
     opt.step()
     return loss.detach()
+
+
+class GraphedTrainStep:
+    """One training step captured in a CUDA graph and replayed: the network's few hundred small launches per
+    step (late stages work on a handful of positions per clip) stop costing host time, which is what bounds the
+    step once the batch is split over several GPUs.  The gradient all-reduce is captured with the rest.
+    Inputs are copied into static buffers before each replay."""
+
+    def __init__(self, model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor, labels: torch.Tensor,
+                 world: int = 1, warmup: int = 3):
+        self.model, self.opt, self.world = model, opt, world
+        self.clips = clips.clone()
+        self.labels = labels.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                       # cuDNN algorithm selection, allocator and optimizer state
+                self._body(set_to_none=False)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._body(set_to_none=False)
+
+    def _body(self, set_to_none: bool):
+        self.opt.zero_grad(set_to_none=set_to_none)
+        loss = F.cross_entropy(self.model(self.clips), self.labels)
+        loss.backward()
+        if self.world > 1:
+            all_reduce_grads(self.model, self.world)
+        self.opt.step()
+        return loss.detach()
+
+    def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if clips is not None:
+            self.clips.copy_(clips, non_blocking=True)
+        if labels is not None:
+            self.labels.copy_(labels, non_blocking=True)
+        self.graph.replay()
+        return self.loss

@@ -54,3 +54,21 @@ def test_bf16_is_deterministic_in_forward():
     a = helpers.run_ours(case, tensors, "bf16")["y"]
     b = helpers.run_ours(case, tensors, "bf16")["y"]
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("name", ["tc2_dg_groups", "tc3_groups", "tc2_c256"])
+def test_separate_bf16_passes_match_fused_backward(name):
+    """dcn_backward_data / dcn_backward_weight (accumulate into zeroed buffers) against dcn_backward (overwrite,
+    shared scratch, forward's channels-last copy taken over)."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    case = {c.name: c for c in cases.TC_CASES}[name]
+    x, w, off, dy, b = [None if t is None else t.cuda() for t in cases.make_inputs(case)]
+    op = dcn.Op(x, w, case.stride, case.pad, case.dil, case.cpg, case.G, precision="bf16")
+    y, fws = op.forward(x, off, w, b, keep_workspace=True)
+    dx_f, doff_f, dw_f, db_f = op.backward(x, off, w, dy, True, True, True, True, fws)
+    dx_s, doff_s = op.backward_data(x, off, w, dy)
+    dw_s, db_s = op.backward_weight(x, off, dy, True, True)
+    dx_n, doff_n, dw_n, _ = op.backward(x, off, w, dy, True, True, True, False, None)     # rebuilds the copy itself
+    _check_status()
+    for a, r in ((dx_f, dx_s), (doff_f, doff_s), (dw_f, dw_s), (db_f, db_s), (dx_n, dx_s), (dw_n, dw_s)):
+        assert cases.rel_err(a.cpu().numpy(), r.cpu().numpy()) <= 1e-3
