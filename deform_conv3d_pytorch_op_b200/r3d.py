@@ -136,9 +136,10 @@ def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor
 
 
 class GraphedTrainStep:
-    """One training step captured in a CUDA graph and replayed: the network's few hundred small launches per
-    step (late stages work on a handful of positions per clip) stop costing host time, which is what bounds the
-    step once the batch is split over several GPUs.  The gradient all-reduce is captured with the rest.
+    """Forward + backward of one training step captured in a CUDA graph and replayed: the network's few hundred
+    small launches per step (late stages work on a handful of positions per clip) stop costing host time, which
+    is what bounds the step once the batch is split over several GPUs.  The gradient all-reduce (a few flat
+    buckets) and the optimizer step run eagerly after the replay, outside the capture.
     Inputs are copied into static buffers before each replay."""
 
     def __init__(self, model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor, labels: torch.Tensor,
@@ -149,21 +150,18 @@ class GraphedTrainStep:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(warmup):                       # cuDNN algorithm selection, allocator and optimizer state
-                self._body(set_to_none=False)
+            for _ in range(warmup):                       # cuDNN algorithm selection, allocator warm-up
+                self._fwd_bwd()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.loss = self._body(set_to_none=False)
+            self.loss = self._fwd_bwd()
 
-    def _body(self, set_to_none: bool):
-        self.opt.zero_grad(set_to_none=set_to_none)
+    def _fwd_bwd(self):
+        self.opt.zero_grad(set_to_none=False)
         loss = F.cross_entropy(self.model(self.clips), self.labels)
         loss.backward()
-        if self.world > 1:
-            all_reduce_grads(self.model, self.world)
-        self.opt.step()
         return loss.detach()
 
     def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -172,4 +170,7 @@ class GraphedTrainStep:
         if labels is not None:
             self.labels.copy_(labels, non_blocking=True)
         self.graph.replay()
+        if self.world > 1:
+            all_reduce_grads(self.model, self.world)
+        self.opt.step()
         return self.loss
