@@ -452,7 +452,13 @@ def main():
         t_gs = 3.0 * wl.bytes_gather_scatter() / (peaks["hbm_gbs"] * 1e9)
         roof.update({"gather_scatter": {"bytes_per_pass": wl.bytes_gather_scatter(), "passes": 3,
                                         "t_roof_ms": t_gs * 1e3, "frac": t_gs / (ms_per_step * 1e-3)}})
-        roof.update({"kernel": dom, "kernel_ms": pass_ms[dom], "traffic": None, "peak_source": peaks["source"],
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "traffic_cfg%d.json" % args.config)
+        if os.path.exists(tpath):            # DRAM bytes of the dominant kernel from the committed ncu capture, scaled
+            with open(tpath) as f:
+                tj = json.load(f)
+            traffic = tj["bytes_per_launch"][dom] * (wl.N * wl.ov) / float(tj["positions"])
+        roof.update({"kernel": dom, "kernel_ms": pass_ms[dom], "traffic": traffic, "peak_source": peaks["source"],
                      "pass_ms": pass_ms,
                      "whole_step_frac": max(wl.flops() / (peaks["bf16_tflops"] * 1e12),
                                             (fwd_b + bwd_b) / (peaks["hbm_gbs"] * 1e9)) / (ms_per_step * 1e-3)})
