@@ -33,7 +33,8 @@ struct Dg2Smem {
     static constexpr int kStageBytes = 3 * kTileBytes;                         // A 16 KB | B 32 KB
     static constexpr int kStagesBytes = kDg2Stages * kStageBytes;
     static constexpr int kColFloats = 32 * 36;                                 // per warp: 32 rows x (32 + 4 pad)
-    static constexpr int kTotFloats = 32 * 12;                                 // per warp: 32 rows x (2^D + 1, padded)
+    static constexpr int kTotStride = 9;                                       // 2^D + 1 totals per row (D = 3)
+    static constexpr int kTotFloats = 32 * kTotStride;                         // per warp (1152 bytes)
     static constexpr int kEntryBytes = 32 * (int)sizeof(DgEntry<D, DEFORM>);   // per warp: 32 rows
     static constexpr int kWarpBytes = (kColFloats + kTotFloats) * 4 + kEntryBytes;
     static constexpr int kBarOffset = kStagesBytes + EW * kWarpBytes;
@@ -51,8 +52,8 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
     using Entry = DgEntry<D, DEFORM>;
     constexpr int NC = 1 << D;
     constexpr int kColsPerWarp = 256 / (EW / 4);
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem_dg2[];     // the kernel has no static shared memory: base is 1024-aligned
+    uint8_t* smem = smem_dg2;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM::kBarOffset);
     uint64_t* empty = full + kDg2Stages;
     uint64_t* acc_full = empty + kDg2Stages;
@@ -173,12 +174,12 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 if (p_ok) {
                     float tv[NC];
 #pragma unroll
-                    for (int e = 0; e < NC; ++e) tv[e] = tot[lane * 12 + e];
+                    for (int e = 0; e < NC; ++e) tv[e] = tot[lane * SM::kTotStride + e];
                     float gr[D];
                     if (pts.valid) {
                         interp_grad<float, D>(pts, tv, gr);
                     } else {
-                        const float stot = tot[lane * 12 + NC];
+                        const float stot = tot[lane * SM::kTotStride + NC];
 #pragma unroll
                         for (int a = 0; a < D; ++a) gr[a] = (D == 3 && g.oob) ? oob_term<float>(g, pts.p[a], stot) : 0.f;
                     }
@@ -234,7 +235,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 #pragma unroll
                     for (int i = 0; i < (int)(sizeof(Entry) / 16); ++i) dst[i] = src[i];
 #pragma unroll
-                    for (int i = 0; i < 3; ++i) reinterpret_cast<float4*>(tot + lane * 12)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int i = 0; i <= NC; ++i) tot[lane * SM::kTotStride + i] = 0.f;
                 }
                 // stage the 32 columns of this thread's position
                 __syncwarp();
@@ -325,23 +326,33 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                             }
                         }
                         const int corner = (NC == 8) ? cq : (cq >> 1);
-                        if (NC == 8 || (cq & 1) == 0) tot[row * 12 + corner] += d[0];
+                        if (NC == 8 || (cq & 1) == 0) tot[row * SM::kTotStride + corner] += d[0];
                         if (D == 3 && g.oob) {
                             sabs += __shfl_xor_sync(0xffffffffu, sabs, 4);
                             sabs += __shfl_xor_sync(0xffffffffu, sabs, 2);
                             sabs += __shfl_xor_sync(0xffffffffu, sabs, 1);
-                            if (cq == 0) tot[row * 12 + NC] += sabs;
+                            if (cq == 0) tot[row * SM::kTotStride + NC] += sabs;
                         }
                     }
                 };
-                RowData ra, rb;
-                fetch(0, ra);
+                if constexpr (D == 2 || !DEFORM || EW == 8) {
+                    RowData ra, rb;
+                    fetch(0, ra);
 #pragma unroll
-                for (int rr = 0; rr < 8; rr += 2) {
-                    fetch(rr + 1, rb);
-                    consume(rr, ra);
-                    if (rr + 2 < 8) fetch(rr + 2, ra);
-                    consume(rr + 1, rb);
+                    for (int rr = 0; rr < 8; rr += 2) {
+                        fetch(rr + 1, rb);
+                        consume(rr, ra);
+                        if (rr + 2 < 8) fetch(rr + 2, ra);
+                        consume(rr + 1, rb);
+                    }
+                } else {
+                    // 3-D with 16 epilogue warps: one row at a time (register budget), the warps overlap each other
+#pragma unroll
+                    for (int rr = 0; rr < 8; ++rr) {
+                        RowData ra;
+                        fetch(rr, ra);
+                        consume(rr, ra);
+                    }
                 }
             }
             flush();
@@ -375,8 +386,8 @@ int launch_tc_dgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, c
     const int u = dgrad_key_unit(g, DEFORM ? 1 : 0);
     if (u == 0) return launch_tc_dgrad_rowwise<D, DEFORM>(g, xcl, off, dpk, wpk, dxcl, doff, st);
     const DgDims d = dg_dims(g);
-    constexpr int EW = (D == 2 || !DEFORM) ? 16 : 8;        // the 3-D epilogue needs the larger register budget
-    const int smem = Dg2Smem<D, DEFORM, EW>::kTotal + 1024;
+    constexpr int EW = 16;
+    const int smem = Dg2Smem<D, DEFORM, EW>::kTotal;
     auto kern = tc_dgrad_kernel<D, DEFORM, EW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     const long long tiles = (long long)g.G * d.PT * d.NB;
