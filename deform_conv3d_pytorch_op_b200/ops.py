@@ -66,7 +66,15 @@ class Op:
                                           tuple(weight.shape[2:]), stride, padding, dilation, group, cpg,
                                           deformable, std_size_rule, oob_offset_grad, pr)
         if prec == "auto":
-            p = mk(_lib.PREC_BF16) if x.dtype == torch.float32 else None
+            # bf16 tensor-core path where the shape allows it and the problem is big enough to pay for its
+            # layout pre-passes (eleven launches per step against three of the exact path)
+            kvol = int(torch.Size(weight.shape[2:]).numel())
+            out_guess = 1
+            for i, k_, s_, p_ in zip(x.shape[2:], weight.shape[2:], _lib._triple(stride, ndim, 1)[3 - ndim:],
+                                     _lib._triple(padding, ndim, 0)[3 - ndim:]):
+                out_guess *= max(1, (i + 2 * p_ - k_) // s_ + 1)
+            flops_per_pass = 2.0 * x.size(0) * weight.size(0) * weight.size(1) * kvol * out_guess
+            p = mk(_lib.PREC_BF16) if (x.dtype == torch.float32 and flops_per_pass >= 1e8) else None
             if p is None or not _lib.lib().dcn_precision_supported(ctypes.byref(p)):
                 p = mk(_lib.PREC_EXACT)
         elif prec in _PRECISIONS:
