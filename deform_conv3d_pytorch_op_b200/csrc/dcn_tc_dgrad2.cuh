@@ -13,8 +13,8 @@
 //            accumulated per lane and, when the key ends, reduced across the lanes of the key with shuffles;
 //   flush    (thread = position again) the 2^D dot products become the D offset-gradient components through
 //            the interpolation-weight derivatives and are added to dOffset, coalesced along positions.
-// Taken when key boundaries fall on multiples of 32 channels (Cg and cpg multiples of 32): every 32-column chunk then
-// belongs to exactly one key.  Other channel-group sizes use the row-wise variant.
+// Taken when key boundaries fall on multiples of U = 32 or 16 channels (U = min(32, cpg, Cg) divides Cg and cpg):
+// a 32-column chunk then holds one or two whole keys.  Other channel-group sizes use the row-wise variant.
 #pragma once
 
 constexpr int kDg2Stages = 2;
@@ -28,29 +28,33 @@ struct alignas(16) DgEntry {
     int pad[2];
 };
 
-template <int D, bool DEFORM, int EW>
+template <int D, bool DEFORM, int EW, int U>
 struct Dg2Smem {
+    static constexpr int kSlots = 32 / U;                                      // keys per 32-column chunk
     static constexpr int kStageBytes = 3 * kTileBytes;                         // A 16 KB | B 32 KB
     static constexpr int kStagesBytes = kDg2Stages * kStageBytes;
     static constexpr int kColFloats = 32 * 36;                                 // per warp: 32 rows x (32 + 4 pad)
     static constexpr int kTotStride = 9;                                       // 2^D + 1 totals per row (D = 3)
-    static constexpr int kTotFloats = 32 * kTotStride;                         // per warp (1152 bytes)
-    static constexpr int kEntryBytes = 32 * (int)sizeof(DgEntry<D, DEFORM>);   // per warp: 32 rows
+    static constexpr int kTotFloats = kSlots * 32 * kTotStride;                // per warp
+    static constexpr int kEntryBytes = kSlots * 32 * (int)sizeof(DgEntry<D, DEFORM>);   // per warp: slots x 32 rows
     static constexpr int kWarpBytes = (kColFloats + kTotFloats) * 4 + kEntryBytes;
     static constexpr int kBarOffset = kStagesBytes + EW * kWarpBytes;
     static constexpr int kTotal = kBarOffset + (2 * kDg2Stages + 4) * 8 + 16;
 };
 
 // EW epilogue warps: 8 (each 128 columns of the tile) or 16 (each 64 columns).
-template <int D, bool DEFORM, int EW>
+// U: channel granularity of the keys, 32 (one key per 32-column chunk) or 16 (two keys per chunk).
+template <int D, bool DEFORM, int EW, int U>
 __global__ void __launch_bounds__(32 * (2 + EW), 1)
 tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                 const uint8_t* __restrict__ dpk, const uint8_t* __restrict__ wpk, float* __restrict__ dxcl,
                 float* __restrict__ doff, const int MT, const int NB, const int NW, const int OC,
                 const long long PC2, const long long PT) {
-    using SM = Dg2Smem<D, DEFORM, EW>;
+    using SM = Dg2Smem<D, DEFORM, EW, U>;
     using Entry = DgEntry<D, DEFORM>;
     constexpr int NC = 1 << D;
+    constexpr int NS = 32 / U;                   // keys (slots) per chunk
+    constexpr int LG = U / 4;                    // lanes that share a key within a row
     constexpr int kColsPerWarp = 256 / (EW / 4);
     extern __shared__ __align__(1024) uint8_t smem_dg2[];     // the kernel has no static shared memory: base is 1024-aligned
     uint8_t* smem = smem_dg2;
@@ -146,6 +150,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         Entry* ent = reinterpret_cast<Entry*>(tot + SM::kTotFloats);                                      // [32]
         const int kq_total = g.kv * g.Cg;
         const int r4 = lane >> 3, cq = lane & 7;        // phase-B coordinates of this lane
+        const int my_slot = (cq * 4) / U;
         const bool want_x = DEFORM && doff != nullptr;
         uint32_t tl = 0;
         bool ok = true;
@@ -163,27 +168,29 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             if (!ok) break;
             tc_fence_after();
 
-            int key = -1;
-            Pt<float, D> pts;
-            pts.valid = false;
+            int key[NS];
+            Pt<float, D> pts[NS];
+#pragma unroll
+            for (int sl = 0; sl < NS; ++sl) { key[sl] = -1; pts[sl].valid = false; }
 
-            // position-owning thread: turn the accumulated dot products of the finished key into offset gradients
-            auto flush = [&]() {
-                if (!DEFORM || doff == nullptr || key < 0) return;
+            // position-owning thread: turn the accumulated dot products of a finished key into offset gradients
+            auto flush = [&](int sl) {
+                if (!DEFORM || doff == nullptr || key[sl] < 0) return;
                 __syncwarp();
                 if (p_ok) {
+                    const float* tp = tot + (sl * 32 + lane) * SM::kTotStride;
                     float tv[NC];
 #pragma unroll
-                    for (int e = 0; e < NC; ++e) tv[e] = tot[lane * SM::kTotStride + e];
+                    for (int e = 0; e < NC; ++e) tv[e] = tp[e];
                     float gr[D];
-                    if (pts.valid) {
-                        interp_grad<float, D>(pts, tv, gr);
+                    if (pts[sl].valid) {
+                        interp_grad<float, D>(pts[sl], tv, gr);
                     } else {
-                        const float stot = tot[lane * SM::kTotStride + NC];
+                        const float stot = tp[NC];
 #pragma unroll
-                        for (int a = 0; a < D; ++a) gr[a] = (D == 3 && g.oob) ? oob_term<float>(g, pts.p[a], stot) : 0.f;
+                        for (int a = 0; a < D; ++a) gr[a] = (D == 3 && g.oob) ? oob_term<float>(g, pts[sl].p[a], stot) : 0.f;
                     }
-                    float* dst = doff + ((size_t)op.n * g.dg * g.kv * D + (size_t)key * D) * g.ov + op.opos;
+                    float* dst = doff + ((size_t)op.n * g.dg * g.kv * D + (size_t)key[sl] * D) * g.ov + op.opos;
 #pragma unroll
                     for (int a = 0; a < D; ++a)
                         if (gr[a] != 0.f) atomicAdd(dst + (size_t)a * g.ov, gr[a]);
@@ -198,31 +205,41 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 tmem_ld_wait();
                 const int kq0 = nb * 256 + col0;
                 if (kq0 >= kq_total) break;
-                uint32_t tap, cl;
-                g.d_Cg.divmod((uint32_t)kq0, tap, cl);
-                const int ch0 = j * g.Cg + (int)cl;                 // first channel of the chunk
-                const int nkey = DEFORM ? (int)g.d_cpg.div((uint32_t)ch0) * g.kv + (int)tap : (int)tap;
-                if (nkey != key) {
-                    flush();
-                    key = nkey;
+                int nkey[NS], ch0[NS];
+#pragma unroll
+                for (int sl = 0; sl < NS; ++sl) {
+                    nkey[sl] = -1; ch0[sl] = 0;
+                    const int kq = kq0 + sl * U;
+                    if (kq < kq_total) {
+                        uint32_t tap, cl;
+                        g.d_Cg.divmod((uint32_t)kq, tap, cl);
+                        ch0[sl] = j * g.Cg + (int)cl;                 // first channel of the slot
+                        nkey[sl] = DEFORM ? (int)g.d_cpg.div((uint32_t)ch0[sl]) * g.kv + (int)tap : (int)tap;
+                    }
+                }
+#pragma unroll
+                for (int sl = 0; sl < NS; ++sl) {
+                    if (nkey[sl] == key[sl]) continue;
+                    flush(sl);
+                    key[sl] = nkey[sl];
                     // phase A: locate the point of the new key and publish it; reset the key's accumulators
                     Entry e;
                     e.n = op.n; e.valid = 0; e.pad[0] = e.pad[1] = 0;
 #pragma unroll
                     for (int i = 0; i < NC; ++i) { e.idx[i] = 0; e.cw[i] = 0.f; }
-                    pts.valid = false;
-                    if (p_ok) {
+                    pts[sl].valid = false;
+                    if (p_ok && nkey[sl] >= 0) {
                         if (DEFORM) {
-                            const int grp = nkey / g.kv, tp = nkey - grp * g.kv;
-                            locate<float, D>(g, off_n, grp, tp, op, pts);
-                            if (pts.valid) {
-                                corner_indices<float, D>(g, pts, e.idx);
-                                corner_weights<float, D>(pts, e.cw);
+                            const int grp = nkey[sl] / g.kv, tp = nkey[sl] - grp * g.kv;
+                            locate<float, D>(g, off_n, grp, tp, op, pts[sl]);
+                            if (pts[sl].valid) {
+                                corner_indices<float, D>(g, pts[sl], e.idx);
+                                corner_weights<float, D>(pts[sl], e.cw);
                                 e.valid = 1;
                             }
                         } else {
                             int pidx;
-                            if (locate_plain<D>(g, nkey, op, pidx)) {
+                            if (locate_plain<D>(g, nkey[sl], op, pidx)) {
                                 e.valid = 1;
                                 e.idx[0] = pidx;
                                 e.cw[0] = 1.f;
@@ -231,11 +248,11 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     }
                     __syncwarp();
                     const int4* src = reinterpret_cast<const int4*>(&e);
-                    int4* dst = reinterpret_cast<int4*>(ent + lane);
+                    int4* dst = reinterpret_cast<int4*>(ent + sl * 32 + lane);
 #pragma unroll
                     for (int i = 0; i < (int)(sizeof(Entry) / 16); ++i) dst[i] = src[i];
 #pragma unroll
-                    for (int i = 0; i <= NC; ++i) tot[lane * SM::kTotStride + i] = 0.f;
+                    for (int i = 0; i <= NC; ++i) tot[(sl * 32 + lane) * SM::kTotStride + i] = 0.f;
                 }
                 // stage the 32 columns of this thread's position
                 __syncwarp();
@@ -244,7 +261,8 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     *reinterpret_cast<uint4*>(colS + lane * 36 + 4 * i) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 __syncwarp();
                 // phase B: the entry and the input values of row iteration rr+1 are fetched while rr is consumed
-                const int cbase = ch0 + cq * 4;                       // first of this lane's 4 channels
+                const int cbase = ch0[my_slot] + (cq * 4) % U;        // first of this lane's 4 channels
+                const bool lane_ok = nkey[my_slot] >= 0;
                 constexpr int NE = DEFORM ? NC : 1;
                 struct RowData {
                     float4 c4;
@@ -255,10 +273,10 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 };
                 auto fetch = [&](int rr, RowData& rd) {
                     const int row = rr * 4 + r4;
-                    const Entry* ep = ent + row;
+                    const Entry* ep = ent + my_slot * 32 + row;
                     const int4 hdr = *reinterpret_cast<const int4*>(&ep->n);      // n, valid, pad, pad
                     rd.c4 = *reinterpret_cast<const float4*>(colS + row * 36 + cq * 4);
-                    rd.valid = hdr.y;
+                    rd.valid = lane_ok ? hdr.y : 0;
                     rd.n = hdr.x;
 #pragma unroll
                     for (int i = 0; i < (NE + 3) / 4; ++i) {
@@ -302,14 +320,15 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                                           make_float4(wv * rd.c4.x, wv * rd.c4.y, wv * rd.c4.z, wv * rd.c4.w));
                             }
                         }
-                    } else if (DEFORM && D == 3 && g.oob) {
+                    } else if (DEFORM && D == 3 && g.oob && lane_ok) {
                         sabs = fabsf(rd.c4.x) + fabsf(rd.c4.y) + fabsf(rd.c4.z) + fabsf(rd.c4.w);
                     }
                     if (want_x) {
-                        // transposing butterfly over the 8 lanes of the row: lane cq ends with the total of one corner
-                        int width = NC;
+                        // transposing butterfly over the LG lanes that share the key: each step halves the set of
+                        // corners a lane is responsible for; `base` is the first corner this lane ends up holding
+                        int width = NC, base = 0;
 #pragma unroll
-                        for (int bit = 4; bit >= 1; bit >>= 1) {
+                        for (int bit = LG / 2; bit >= 1; bit >>= 1) {
                             if (width > 1) {
                                 const int hw = width / 2;
 #pragma unroll
@@ -320,18 +339,24 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                                         d[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
                                     }
                                 }
+                                if (cq & bit) base += hw;
                                 width = hw;
                             } else {
                                 d[0] += __shfl_xor_sync(0xffffffffu, d[0], bit);
                             }
                         }
-                        const int corner = (NC == 8) ? cq : (cq >> 1);
-                        if (NC == 8 || (cq & 1) == 0) tot[row * SM::kTotStride + corner] += d[0];
+                        // lanes that hold a duplicate after the plain-add steps (2-D with 8 lanes) stay silent
+                        const bool writer = (NC >= LG) || ((cq & (LG / NC - 1)) == 0);
+                        if (writer) {
+                            float* tp = tot + (my_slot * 32 + row) * SM::kTotStride + base;
+#pragma unroll
+                            for (int i = 0; i < NC; ++i)
+                                if (i < width) tp[i] += d[i];
+                        }
                         if (D == 3 && g.oob) {
-                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 4);
-                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 2);
-                            sabs += __shfl_xor_sync(0xffffffffu, sabs, 1);
-                            if (cq == 0) tot[row * SM::kTotStride + NC] += sabs;
+#pragma unroll
+                            for (int bit = LG / 2; bit >= 1; bit >>= 1) sabs += __shfl_xor_sync(0xffffffffu, sabs, bit);
+                            if ((cq & (LG - 1)) == 0) tot[(my_slot * 32 + row) * SM::kTotStride + NC] += sabs;
                         }
                     }
                 };
@@ -355,7 +380,8 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     }
                 }
             }
-            flush();
+#pragma unroll
+            for (int sl = 0; sl < NS; ++sl) flush(sl);
             tc_fence_before();
             mbar_arrive(&acc_empty[b]);
         }
@@ -374,24 +400,32 @@ inline int dgrad_key_unit(const Geom& g, int deform) {
     int u = 32;
     if (g.Cg < u) u = g.Cg;
     if (deform && g.cpg < u) u = g.cpg;
-    if (u != 32) return 0;      // with 16-channel keys the per-key hand-over costs more than the aggregation saves
+    if (u != 32 && u != 16) return 0;
     if (g.Cg % u != 0) return 0;
     if (deform && g.cpg % u != 0) return 0;
     return u;
+}
+
+template <int D, bool DEFORM, int EW, int U>
+int launch_tc_dgrad_t(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk,
+                      const uint8_t* wpk, float* dxcl, float* doff, cudaStream_t st) {
+    const DgDims d = dg_dims(g);
+    const int smem = Dg2Smem<D, DEFORM, EW, U>::kTotal;
+    static_assert(Dg2Smem<D, DEFORM, EW, U>::kTotal <= kSmemLimit, "dgrad epilogue staging does not fit");
+    auto kern = tc_dgrad_kernel<D, DEFORM, EW, U>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
+    const long long tiles = (long long)g.G * d.PT * d.NB;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, 32 * (2 + EW), smem, st>>>(g, xcl, off, dpk, wpk, dxcl, doff, d.MT, d.NB, d.NW, d.OC, d.PC2, d.PT);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 template <int D, bool DEFORM>
 int launch_tc_dgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* dpk,
                     const uint8_t* wpk, float* dxcl, float* doff, cudaStream_t st) {
     const int u = dgrad_key_unit(g, DEFORM ? 1 : 0);
-    if (u == 0) return launch_tc_dgrad_rowwise<D, DEFORM>(g, xcl, off, dpk, wpk, dxcl, doff, st);
-    const DgDims d = dg_dims(g);
-    constexpr int EW = 16;
-    const int smem = Dg2Smem<D, DEFORM, EW>::kTotal;
-    auto kern = tc_dgrad_kernel<D, DEFORM, EW>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
-    const long long tiles = (long long)g.G * d.PT * d.NB;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, 32 * (2 + EW), smem, st>>>(g, xcl, off, dpk, wpk, dxcl, doff, d.MT, d.NB, d.NW, d.OC, d.PC2, d.PT);
-    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+    if (u == 32) return launch_tc_dgrad_t<D, DEFORM, 16, 32>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+    // two keys per chunk double the per-warp staging: 8 epilogue warps
+    if (u == 16) return launch_tc_dgrad_t<D, DEFORM, 8, 16>(g, xcl, off, dpk, wpk, dxcl, doff, st);
+    return launch_tc_dgrad_rowwise<D, DEFORM>(g, xcl, off, dpk, wpk, dxcl, doff, st);
 }
