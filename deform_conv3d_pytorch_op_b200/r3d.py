@@ -166,7 +166,7 @@ class GraphedTrainStep:
 
     def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
         if clips is not None:
-            self.clips.copy_(clips, non_blocking=True)
+            self.clips.copy_(clips, non_blocking=True)      # keeps the static buffer's memory format
         if labels is not None:
             self.labels.copy_(labels, non_blocking=True)
         self.graph.replay()
