@@ -31,6 +31,13 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for the whole warp: every lane's earlier shared-memory writes are ordered before it by the warp
+// barrier.  An mbarrier arrival is a serialised update of one shared-memory word, so per-thread arrivals of
+// hundreds of threads per pipeline stage cost thousands of cycles; per-warp arrivals do not.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(smem_u32(bar)),
                  "r"(bytes)
@@ -68,6 +75,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return true;
 }
+
+// Position in a ring of n buffers plus the phase parity of its barriers, advanced without division
+// (the ring sizes are run-time values; an integer division per pipeline stage and thread is not cheap).
+struct Ring {
+    uint32_t i = 0, ph = 0;
+    __device__ __forceinline__ void next(uint32_t n) {
+        if (++i == n) { i = 0; ph ^= 1u; }
+    }
+};
 
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -103,7 +103,7 @@ tc_dgrad_rowwise_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kDgEpiWarps * 32);
+            mbar_init(&acc_empty[b], kDgEpiWarps);
         }
         fence_barrier_init();
     }
@@ -286,7 +286,7 @@ tc_dgrad_rowwise_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, con
             }
             flush();
             tc_fence_before();
-            mbar_arrive(&acc_empty[b]);
+            mbar_arrive_warp(&acc_empty[b]);
         }
     }
 

@@ -73,7 +73,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], EW * 32);
+            mbar_init(&acc_empty[b], EW);
         }
         fence_barrier_init();
     }
@@ -383,7 +383,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 #pragma unroll
             for (int sl = 0; sl < NS; ++sl) flush(sl);
             tc_fence_before();
-            mbar_arrive(&acc_empty[b]);
+            mbar_arrive_warp(&acc_empty[b]);
         }
     }
 

@@ -49,16 +49,16 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl->full[s], GW * 32 + 1);
+            mbar_init(&ctl->full[s], GW + 1);            // one arrival per gather warp + the loader
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], kEpilogueWarps * 32);
+            mbar_init(&ctl->acc_empty[b], kEpilogueWarps);
         }
         for (int b = 0; b < kMaxTabs; ++b) {
-            mbar_init(&ctl->tab_full[b], kCoordWarps * 32);
-            mbar_init(&ctl->tab_empty[b], GW * 32);
+            mbar_init(&ctl->tab_full[b], kCoordWarps);
+            mbar_init(&ctl->tab_empty[b], GW);
         }
         fence_barrier_init();
     }
@@ -77,7 +77,8 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     if (warp == 0) {
         // ------------------------------------------------ MMA issue
         if (lane == 0) {
-            uint32_t it = 0, tl = 0;
+            uint32_t tl = 0;
+            Ring rs;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
                 const int ks = (int)(t % KS);
@@ -88,9 +89,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const uint32_t b = tl & 1;
                 ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
                 tc_fence_after();
-                for (int kc = kc0; kc < kc1 && ok; ++kc, ++it) {
-                    const uint32_t s = it % n_stages;
-                    ok = mbar_wait(&ctl->full[s], (it / n_stages) & 1);
+                for (int kc = kc0; kc < kc1 && ok; ++kc, rs.next(n_stages)) {
+                    const uint32_t s = rs.i;
+                    ok = mbar_wait(&ctl->full[s], rs.ph);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_base = smem_u32(smem + s * kFwdStageBytes);
@@ -111,7 +112,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     } else if (warp == 1) {
         // ------------------------------------------------ weight loader
         if (lane == 0) {
-            uint32_t it = 0;
+            Ring rs;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const int ks = (int)(t % KS);
@@ -120,9 +121,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const int j = (int)(tt / PT / MB);
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
                 const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
-                for (int kc = kc0; kc < kc1 && ok; ++kc, ++it) {
-                    const uint32_t s = it % n_stages;
-                    ok = mbar_wait(&ctl->empty[s], ((it / n_stages) & 1) ^ 1);
+                for (int kc = kc0; kc < kc1 && ok; ++kc, rs.next(n_stages)) {
+                    const uint32_t s = rs.i;
+                    ok = mbar_wait(&ctl->empty[s], rs.ph ^ 1u);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)(mtb * kTileBytes));
                     for (int mt = 0; mt < mtb; ++mt) {
@@ -197,13 +198,14 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         prefetch(pre, 0); advance(pre);
         prefetch(pre, 1); advance(pre);
         uint32_t it = 0;
+        Ring rt;
         bool ok = true;
         while (cur.t < n_tiles && ok) {
             prefetch(pre, it + 2); advance(pre);
             cp_async_wait<2>();
-            const uint32_t tb = it % n_tabs;
+            const uint32_t tb = rt.i;
             const SlotInfo si = stage_slots(cur);
-            ok = mbar_wait(&ctl->tab_empty[tb], ((it / n_tabs) & 1) ^ 1);
+            ok = mbar_wait(&ctl->tab_empty[tb], rt.ph ^ 1u);
             if (!ok) break;
             if (warp == 2 && lane < 8) ctl->slot_of_chunk[tb][lane] = si.my_slot;
             const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 128;
@@ -219,9 +221,10 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                                                tab + ((size_t)tb * max_slots + sl) * 128 + ctid + 64 * i);
                 }
             }
-            mbar_arrive(&ctl->tab_full[tb]);
+            mbar_arrive_warp(&ctl->tab_full[tb]);
             advance(cur);
             ++it;
+            rt.next(n_tabs);
         }
         cp_async_wait<0>();
     } else if (warp < 2 + kCoordWarps + GW) {
@@ -234,21 +237,21 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         constexpr int NQ = DEFORM ? (1 << D) : 1;
         constexpr int RT = 128 * 8 / (GW * 32);                    // rows per thread and stage: 4 or 2
         constexpr int RS = GW * 4;                                 // row stride between a thread's rows
-        constexpr int RPP = RT / 2;                                // rows per pass (one row per pass: +31 % time)
-        constexpr int PPS = 2;                                     // passes per stage
+        constexpr int RPP = (GW == 16) ? RT : RT / 2;              // rows per pass (one row per pass: +31 % time)
+        constexpr int PPS = RT / RPP;                              // passes per stage
         // 2-D: the next pass is issued before the current one is finished (16 loads in flight);
         // 3-D: one pass at a time already has 16 loads in flight, and two would not fit the register file.
-        constexpr bool kOverlap = (D == 2 || !DEFORM);
+        constexpr bool kOverlap = (D == 2 || !DEFORM) && GW == 8;
         struct Pass {
             uint4 q[RPP][NQ];
             float w[RPP][NQ];
-            uint32_t it;
+            uint32_t s, ph;     // operand stage of this pass and the phase of its barriers
             int h;
         };
         // issue cursor
         long long ct = blockIdx.x;
         int ckc = 0, ckc_end = 0, ch = 0, cj = 0, cc = 0, csl = 0;
-        uint32_t cit = 0;
+        Ring rtab, rstg;            // table buffer and operand stage of the issue cursor
         size_t nbase[RT];
         bool failed = false;
         auto init_tile = [&]() {
@@ -269,9 +272,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         if (ct < n_tiles) init_tile();
         auto issue = [&](Pass& p) -> bool {
             if (ct >= n_tiles || failed) return false;
-            const uint32_t tb = cit % n_tabs;
+            const uint32_t tb = rtab.i;
             if (ch == 0) {
-                if (!mbar_wait(&ctl->tab_full[tb], (cit / n_tabs) & 1)) { failed = true; return false; }
+                if (!mbar_wait(&ctl->tab_full[tb], rtab.ph)) { failed = true; return false; }
                 csl = ctl->slot_of_chunk[tb][chunk];
                 const int kp = ckc * kTileK + chunk * 8;
                 uint32_t tap, cl;
@@ -289,12 +292,14 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                     }
                 }
             }
-            p.it = cit;
+            p.s = rstg.i;
+            p.ph = rstg.ph;
             p.h = ch;
-            if (ch == PPS - 1) mbar_arrive(&ctl->tab_empty[tb]);     // this thread is done with the stage's table
+            if (ch == PPS - 1) mbar_arrive_warp(&ctl->tab_empty[tb]);   // this warp is done with the stage's table
             if (++ch == PPS) {
                 ch = 0;
-                ++cit;
+                rtab.next(n_tabs);
+                rstg.next(n_stages);
                 if (++ckc == ckc_end) {
                     ct += gridDim.x;
                     if (ct < n_tiles) init_tile();
@@ -303,9 +308,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             return true;
         };
         auto finish = [&](Pass& p) -> bool {
-            const uint32_t s = p.it % n_stages;
+            const uint32_t s = p.s;
             if (p.h == 0) {
-                if (!mbar_wait(&ctl->empty[s], ((p.it / n_stages) & 1) ^ 1)) { failed = true; return false; }
+                if (!mbar_wait(&ctl->empty[s], p.ph ^ 1u)) { failed = true; return false; }
             }
             const uint32_t b_base = smem_u32(smem + s * kFwdStageBytes + 2 * kTileBytes);
 #pragma unroll
@@ -315,7 +320,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             }
             if (p.h == PPS - 1) {
                 fence_proxy_async_smem();
-                mbar_arrive(&ctl->full[s]);
+                mbar_arrive_warp(&ctl->full[s]);
             }
             return true;
         };
@@ -391,7 +396,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 }
             }
             tc_fence_before();
-            mbar_arrive(&ctl->acc_empty[b]);
+            mbar_arrive_warp(&ctl->acc_empty[b]);
         }
     }
 
@@ -444,7 +449,7 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 3) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
     const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
-    constexpr int GW = 8;      // 16 gather warps (2 rows each) measured slower: 0.62 ms vs 0.53 ms on the 2-D benchmark shape
+    constexpr int GW = 8;      // 16 gather warps (2 rows each) measured slower on the 2-D benchmark shape
     auto kern = tc_forward_kernel<D, DEFORM, GW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     // split the K range when there are fewer tiles than SMs (small batches / late layers of a network)

@@ -42,12 +42,12 @@ tc_forward_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kDirectStages; ++s) {
-            mbar_init(&full[s], kProducerWarps * 32 + 1);
+            mbar_init(&full[s], kProducerWarps + 1);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], kEpilogueWarps * 32);
+            mbar_init(&acc_empty[b], kEpilogueWarps);
         }
         fence_barrier_init();
     }
@@ -154,7 +154,7 @@ tc_forward_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, co
                 for (int i = 0; i < 4; ++i)
                     st_shared_v4(b_base + swz_offset(row0 + 32 * i, chunk), v[i].x, v[i].y, v[i].z, v[i].w);
                 fence_proxy_async_smem();
-                mbar_arrive(&full[s]);
+                mbar_arrive_warp(&full[s]);
             }
         }
     } else {
@@ -207,7 +207,7 @@ tc_forward_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, co
                 }
             }
             tc_fence_before();
-            mbar_arrive(&acc_empty[b]);
+            mbar_arrive_warp(&acc_empty[b]);
         }
     }
 

@@ -75,7 +75,7 @@ tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWgStages; ++s) {
-            mbar_init(&full[s], kProducerWarps * 32 + 1);
+            mbar_init(&full[s], kProducerWarps + 1);
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -161,7 +161,7 @@ tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, cons
                     st_shared_v4(b_base + swz_offset(row0 + 8 * i, cj % 8), v[i].x, v[i].y, v[i].z, v[i].w);
             }
             fence_proxy_async_smem();
-            mbar_arrive(&full[s]);
+            mbar_arrive_warp(&full[s]);
         }
     } else {
         const int q = warp & 3;

@@ -50,13 +50,13 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl->full[s], kGatherWarps * 32 + 1);
+            mbar_init(&ctl->full[s], kGatherWarps + 1);
             mbar_init(&ctl->empty[s], 1);
         }
         mbar_init(&ctl->acc_full, 1);
         for (int b = 0; b < kMaxTabs; ++b) {
-            mbar_init(&ctl->tab_full[b], kCoordWarps * 32);
-            mbar_init(&ctl->tab_empty[b], kGatherWarps * 32);
+            mbar_init(&ctl->tab_full[b], kCoordWarps);
+            mbar_init(&ctl->tab_empty[b], kGatherWarps);
         }
         fence_barrier_init();
     }
@@ -86,9 +86,10 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
-            for (int it = 0; it < n_chunks && ok; ++it) {
-                const uint32_t s = it % n_stages;
-                ok = mbar_wait(&ctl->full[s], (it / n_stages) & 1);
+            Ring rs;
+            for (int it = 0; it < n_chunks && ok; ++it, rs.next(n_stages)) {
+                const uint32_t s = rs.i;
+                ok = mbar_wait(&ctl->full[s], rs.ph);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_base = smem_u32(smem + (size_t)s * stage_bytes);
@@ -108,9 +109,10 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = true;
-            for (int it = 0; it < n_chunks && ok; ++it) {
-                const uint32_t s = it % n_stages;
-                ok = mbar_wait(&ctl->empty[s], ((it / n_stages) & 1) ^ 1);
+            Ring rs;
+            for (int it = 0; it < n_chunks && ok; ++it, rs.next(n_stages)) {
+                const uint32_t s = rs.i;
+                ok = mbar_wait(&ctl->empty[s], rs.ph ^ 1u);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&ctl->full[s], (uint32_t)(mtb * kTileBytes));
                 for (int mt = 0; mt < mtb; ++mt) {
@@ -143,14 +145,15 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         prefetch(0);
         prefetch(1);
         bool ok = true;
-        for (int it = 0; it < n_chunks && ok; ++it) {
+        Ring rt;
+        for (int it = 0; it < n_chunks && ok; ++it, rt.next(n_tabs)) {
             prefetch(it + 2);
             cp_async_wait<2>();
-            const uint32_t tb = it % n_tabs;
+            const uint32_t tb = rt.i;
             const long long P = (c_begin + it) * 64 + row;
             const bool pok = P < g.P;
             const OutPos op = decompose_pos(g, pok ? P : 0);
-            ok = mbar_wait(&ctl->tab_empty[tb], ((it / n_tabs) & 1) ^ 1);
+            ok = mbar_wait(&ctl->tab_empty[tb], rt.ph ^ 1u);
             if (!ok) break;
             const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 64;
             for (int sl = 0; sl < nslots; ++sl) {
@@ -160,7 +163,7 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 for (int a = 0; a < D; ++a) offv[a] = (DEFORM && key >= 0 && pok) ? src[(size_t)(sl * D + a) * 64 + row] : 0.f;
                 fill_entry_from<D, DEFORM>(g, offv, op, pok, key, tab + ((size_t)tb * max_slots + sl) * 64 + row);
             }
-            mbar_arrive(&ctl->tab_full[tb]);
+            mbar_arrive_warp(&ctl->tab_full[tb]);
         }
         cp_async_wait<0>();
     } else if (warp < 2 + kCoordWarps + kGatherWarps) {
@@ -180,15 +183,17 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
         struct Pass {
             uint4 q[RPP][NQ];
             float w[RPP][NQ];
-            int it, h;
+            uint32_t s, ph;
+            int h;
         };
         int cit = 0, ch = 0;
+        Ring rtab, rstg;
         bool failed = false;
         auto issue = [&](Pass& p) -> bool {
             if (cit >= n_chunks || failed) return false;
-            const uint32_t tb = cit % n_tabs;
+            const uint32_t tb = rtab.i;
             if (ch == 0) {
-                if (!mbar_wait(&ctl->tab_full[tb], (cit / n_tabs) & 1)) { failed = true; return false; }
+                if (!mbar_wait(&ctl->tab_full[tb], rtab.ph)) { failed = true; return false; }
             }
             const Entry* trow = tab + ((size_t)tb * max_slots + sl) * 64;
 #pragma unroll
@@ -204,16 +209,17 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     for (int e = 0; e < NQ; ++e) { p.q[r][e] = make_uint4(0, 0, 0, 0); p.w[r][e] = 0.f; }
                 }
             }
-            p.it = cit;
+            p.s = rstg.i;
+            p.ph = rstg.ph;
             p.h = ch;
-            if (ch == PPS - 1) mbar_arrive(&ctl->tab_empty[tb]);
-            if (++ch == PPS) { ch = 0; ++cit; }
+            if (ch == PPS - 1) mbar_arrive_warp(&ctl->tab_empty[tb]);
+            if (++ch == PPS) { ch = 0; ++cit; rtab.next(n_tabs); rstg.next(n_stages); }
             return true;
         };
         auto finish = [&](Pass& p) -> bool {
-            const uint32_t s = p.it % n_stages;
+            const uint32_t s = p.s;
             if (p.h == 0) {
-                if (!mbar_wait(&ctl->empty[s], ((p.it / n_stages) & 1) ^ 1)) { failed = true; return false; }
+                if (!mbar_wait(&ctl->empty[s], p.ph ^ 1u)) { failed = true; return false; }
             }
             if (col_ok) {
                 const uint32_t b_base = smem_u32(smem + (size_t)s * stage_bytes) + sub_off;
@@ -225,7 +231,7 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             }
             if (p.h == PPS - 1) {
                 fence_proxy_async_smem();
-                mbar_arrive(&ctl->full[s]);
+                mbar_arrive_warp(&ctl->full[s]);
             }
             return true;
         };
