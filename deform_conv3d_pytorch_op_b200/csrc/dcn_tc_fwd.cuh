@@ -2,33 +2,55 @@
 //
 //   y[o, P] = sum over k' of W[o, k'] * sample(k', P)  (+ bias)            k' = tap * Cg + c
 //
-// Persistent CTAs, one per SM; 16 warps:
+// Persistent CTAs, one per SM; 6 + GW warps:
 //   warp 0       MMA issue (one elected lane) and tensor-memory allocation
 //   warp 1       weight-tile loader (bulk async copies, one elected lane)
-//   warps 2-3    coordinate warps (dcn_tc_sampler.cuh)
-//   warps 4-11   gather warps: build the sampled, interpolated patch tile straight into the swizzled B operand
-//   warps 12-15  epilogue: tensor memory -> registers -> (+bias) -> y
+//   warps 2-5    coordinate warps (dcn_tc_sampler.cuh).  Warp k fills the whole table of every 4th pipeline stage
+//                (k, k+4, ...): the chain offsets -> coordinates -> corner table of one stage is long and serial,
+//                so four stages are in production at once.  The same warps drain finished accumulators
+//                (tensor memory -> registers -> (+bias) -> y) whenever they have no table to fill, so the
+//                epilogue costs no warps of its own.
+//   warps 6..    GW gather warps: build the sampled, interpolated patch tile straight into the swizzled B
+//                operand, all of them on the same stage (splitting them into groups that take alternate
+//                stages measured slower).
 // Tile = (conv group, block of up to 256 output channels, 128 output positions).  The sampled operand of a
 // K chunk is shared by both 128-row halves of the output-channel block.
 #pragma once
 
+// Cycle accounting of the roles (build with -DDCN_PROFILE; read with dcn_debug_fwd_profile): per role the
+// cycles spent in its waits and in total, taken on CTA 0.  Compiled out of the product build.
+#ifdef DCN_PROFILE
+__device__ unsigned long long g_fwd_prof[32];
+#define PROF_DECL long long pw_[4] = {0, 0, 0, 0}; const long long pstart_ = clock64();
+#define PROF_T0 const long long pc0_ = clock64();
+#define PROF_ADD(k) pw_[k] += clock64() - pc0_;
+#define PROF_OUT(role, cond) if (blockIdx.x == 0 && (cond)) { for (int z_ = 0; z_ < 4; ++z_) g_fwd_prof[(role) * 5 + z_] = pw_[z_]; g_fwd_prof[(role) * 5 + 4] = clock64() - pstart_; }
+#else
+#define PROF_DECL
+#define PROF_T0
+#define PROF_ADD(k)
+#define PROF_OUT(role, cond)
+#endif
+
 constexpr int kMaxStages = 4;
+constexpr int kFwdCoordWarps = 4;               // forward: coordinate + epilogue warps, one per tensor-memory lane quarter
 constexpr int kCoordWarps = 2;
 constexpr int kGatherWarps = 8;
-constexpr int fwd_threads(int gw) { return 32 * (2 + kCoordWarps + gw + kEpilogueWarps); }
+constexpr int fwd_threads(int gw) { return 32 * (2 + kFwdCoordWarps + gw); }
 constexpr int kFwdStageBytes = 3 * kTileBytes;      // A0 | A1 | B
 constexpr int kSmemLimit = 232448;                   // 227 KB opt-in maximum per CTA
 
-constexpr int kMaxTabs = 3;
-constexpr int kOffRing = 3;          // offset prefetch distance of the coordinate warps + 1
+constexpr int kMaxTabs = 3;          // weight-gradient kernel: table ring
+constexpr int kOffRing = 3;          // weight-gradient kernel: offset prefetch distance of the coordinate warps + 1
+constexpr int kFwdMaxTabs = 6;
+constexpr int kFwdOffRing = 2 * kFwdCoordWarps;   // two private offset staging buffers per coordinate warp
 
 struct FwdCtl {            // lives behind the stages, the tables and the offset staging ring
-    uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2], tab_full[kMaxTabs], tab_empty[kMaxTabs];
+    uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2], tab_full[kFwdMaxTabs], tab_empty[kFwdMaxTabs];
     uint32_t tmem_base;
-    int slot_of_chunk[kMaxTabs][8];
+    int slot_of_chunk[kFwdMaxTabs][8];
 };
 
-// GW gather warps: 8 (4 rows per thread and stage) or 16 (2 rows; more warps to hide the gather latency).
 template <int D, bool DEFORM, int GW>
 __global__ void __launch_bounds__(fwd_threads(GW), 1)
 tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
@@ -42,8 +64,8 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     Entry* tab = reinterpret_cast<Entry*>(smem + n_stages * kFwdStageBytes);          // [n_tabs][max_slots][128]
     float* ostage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tab) +
-                                             (size_t)n_tabs * max_slots * 128 * sizeof(Entry));   // [3][max_slots][D][128]
-    FwdCtl* ctl = reinterpret_cast<FwdCtl*>(ostage + (size_t)kOffRing * max_slots * D * 128);
+                                             (size_t)n_tabs * max_slots * 128 * sizeof(Entry));   // [kFwdOffRing][max_slots][D][128]
+    FwdCtl* ctl = reinterpret_cast<FwdCtl*>(ostage + (size_t)kFwdOffRing * max_slots * D * 128);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
@@ -54,11 +76,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], kEpilogueWarps);
+            mbar_init(&ctl->acc_empty[b], kFwdCoordWarps);
         }
-        for (int b = 0; b < kMaxTabs; ++b) {
-            mbar_init(&ctl->tab_full[b], kCoordWarps);
-            mbar_init(&ctl->tab_empty[b], GW);
+        for (int b = 0; b < kFwdMaxTabs; ++b) {
+            mbar_init(&ctl->tab_full[b], 1);             // the coordinate warp that filled it
+            mbar_init(&ctl->tab_empty[b], GW);           // the gather warps that read it
         }
         fence_barrier_init();
     }
@@ -77,6 +99,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     if (warp == 0) {
         // ------------------------------------------------ MMA issue
         if (lane == 0) {
+            PROF_DECL
             uint32_t tl = 0;
             Ring rs;
             bool ok = true;
@@ -87,11 +110,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
                 const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
                 const uint32_t b = tl & 1;
-                ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
+                { PROF_T0 ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1); PROF_ADD(0) }
                 tc_fence_after();
                 for (int kc = kc0; kc < kc1 && ok; ++kc, rs.next(n_stages)) {
                     const uint32_t s = rs.i;
-                    ok = mbar_wait(&ctl->full[s], rs.ph);
+                    { PROF_T0 ok = mbar_wait(&ctl->full[s], rs.ph); PROF_ADD(1) }
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_base = smem_u32(smem + s * kFwdStageBytes);
@@ -108,6 +131,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 }
                 if (ok) umma_commit(&ctl->acc_full[b]);
             }
+            PROF_OUT(0, true)
         }
     } else if (warp == 1) {
         // ------------------------------------------------ weight loader
@@ -133,36 +157,31 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 }
             }
         }
-    } else if (warp < 2 + kCoordWarps) {
-        // ------------------------------------------------ coordinate warps
-        // Offsets are prefetched two stages ahead with 4-byte cp.async into a private staging ring, so the
-        // offset-load latency never sits on the critical path of a stage.
-        const int ctid = threadIdx.x - 64;          // 0..63, rows ctid and ctid + 64
+    } else if (warp < 2 + kFwdCoordWarps) {
+        // ------------------------------------------------ coordinate + epilogue warps
+        const int cw = warp - 2;                    // takes stages cw, cw + 4, ... of this CTA's stage sequence
+        const int q = warp & 3;                     // tensor-memory lane quarter this warp may access
+        constexpr int CR = 4;                       // table rows per thread: lane + 32 * i
         struct Cur {
-            long long t;
+            long long t, pt;
             int kc, kc_end, j;
-            OutPos op[2];
-            bool pok[2];
+            uint32_t tl;            // how many tiles of this CTA came before t
         };
         auto init_tile = [&](Cur& c) {
             const int ks = (int)(c.t % KS);
             const long long tt = c.t / KS;
-            const long long pt = tt % PT;
+            c.pt = tt % PT;
             c.j = (int)(tt / PT / MB);
             c.kc = ks * cpk;
             c.kc_end = (c.kc + cpk < KC) ? c.kc + cpk : KC;
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const long long P = pt * kTileN + ctid + 64 * i;
-                c.pok[i] = P < g.P;
-                c.op[i] = decompose_pos(g, c.pok[i] ? P : 0);
-            }
         };
-        auto advance = [&](Cur& c) {
-            if (c.t >= n_tiles) return;
-            if (++c.kc == c.kc_end) {
-                c.t += gridDim.x;
-                if (c.t < n_tiles) init_tile(c);
+        auto skip = [&](Cur& c, int n) {            // n stages further
+            for (int i = 0; i < n && c.t < n_tiles; ++i) {
+                if (++c.kc == c.kc_end) {
+                    c.t += gridDim.x;
+                    ++c.tl;
+                    if (c.t < n_tiles) init_tile(c);
+                }
             }
         };
         auto stage_slots = [&](const Cur& c) {
@@ -170,103 +189,199 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             const int key = chunk_key(g, c.j, c.kc * kTileK + (lane & 7) * 8, tap_, c_);
             return make_slots(key, lane, 8);
         };
-        auto prefetch = [&](const Cur& c, uint32_t itp) {
+        // Offsets of a stage are fetched with 4-byte cp.async into one of this warp's two staging buffers while
+        // the warp's previous stage is being filled, so their latency is off the critical path.
+        float* my_ost = ostage + (size_t)cw * 2 * max_slots * D * 128;
+        auto prefetch = [&](const Cur& c, uint32_t buf) {
             if (DEFORM && c.t < n_tiles) {
                 const SlotInfo si = stage_slots(c);
-                float* dst = ostage + (size_t)(itp % kOffRing) * max_slots * D * 128;
+                float* dst = my_ost + (size_t)buf * max_slots * D * 128;
                 for (int sl = 0; sl < si.nslots; ++sl) {
                     const int key = slot_key(si, sl);
                     if (key < 0) continue;
                     const int grp = key / g.kv, tap = key - grp * g.kv;
 #pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        if (!c.pok[i]) continue;
-                        const float* src = offset_ptr<float, D>(g, off + (size_t)c.op[i].n * g.dg * g.kv * D * g.ov,
-                                                                grp, tap, c.op[i]);
+                    for (int i = 0; i < CR; ++i) {
+                        const long long P = c.pt * kTileN + lane + 32 * i;
+                        if (P >= g.P) continue;
+                        const OutPos op = decompose_pos(g, P);
+                        const float* src = offset_ptr<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op);
 #pragma unroll
                         for (int a = 0; a < D; ++a)
-                            cp_async4(dst + (size_t)(sl * D + a) * 128 + ctid + 64 * i, src + (size_t)a * g.ov);
+                            cp_async4(dst + (size_t)(sl * D + a) * 128 + lane + 32 * i, src + (size_t)a * g.ov);
                     }
                 }
             }
             cp_async_commit();
         };
-        Cur cur, pre;
-        cur.t = blockIdx.x; cur.kc = 0; cur.kc_end = 0;
+        Cur cur;
+        cur.t = blockIdx.x; cur.pt = 0; cur.kc = 0; cur.kc_end = 0; cur.j = 0; cur.tl = 0;
         if (cur.t < n_tiles) init_tile(cur);
-        pre = cur;
-        prefetch(pre, 0); advance(pre);
-        prefetch(pre, 1); advance(pre);
-        uint32_t it = 0;
+        skip(cur, cw);
         Ring rt;
-        bool ok = true;
-        while (cur.t < n_tiles && ok) {
-            prefetch(pre, it + 2); advance(pre);
-            cp_async_wait<2>();
-            const uint32_t tb = rt.i;
-            const SlotInfo si = stage_slots(cur);
-            ok = mbar_wait(&ctl->tab_empty[tb], rt.ph ^ 1u);
-            if (!ok) break;
-            if (warp == 2 && lane < 8) ctl->slot_of_chunk[tb][lane] = si.my_slot;
-            const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 128;
-            for (int sl = 0; sl < si.nslots; ++sl) {
-                const int key = slot_key(si, sl);
+        for (int i = 0; i < cw; ++i) rt.next(n_tabs);
+        prefetch(cur, 0);
+        {
+            Cur pre = cur;
+            skip(pre, kFwdCoordWarps);
+            prefetch(pre, 1);
+        }
+        uint32_t it = 0;                // stages this warp has filled
+        long long et = blockIdx.x;      // next tile whose accumulator this warp drains
+        uint32_t etl = 0;               // ... and how many tiles of this CTA came before it
+        bool waiting = false;
+        long long t0 = 0;
+        PROF_DECL
+        while (true) {
+            const bool more = cur.t < n_tiles;
+            if (!more && et >= n_tiles) break;
+            const bool tab_free = more && mbar_try_wait(&ctl->tab_empty[rt.i], rt.ph ^ 1u);
+            // Drain an accumulator when there is no table to fill (the ring is full, or the tables are done) or
+            // when the tables of the tile that needs the accumulator's buffer are about to be filled.
+            if (et < n_tiles && (!tab_free || cur.tl >= etl + 2) &&
+                mbar_try_wait(&ctl->acc_full[etl & 1], (etl >> 1) & 1)) {
+                PROF_T0
+                waiting = false;
+                tc_fence_after();
+                const uint32_t b = etl & 1;
+                const int ks = (int)(et % KS);
+                const long long tt = et / KS;
+                const long long pt = tt % PT;
+                const int mb = (int)((tt / PT) % MB);
+                const int j = (int)(tt / PT / MB);
+                const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
+                for (int mt = 0; mt < mtb; ++mt) {
+                    const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;      // output channel within the group
+                    const bool o_ok = ol < g.Og;
+                    const int o = j * g.Og + ol;
+                    const float bv = (bias != nullptr && o_ok && ks == 0) ? __ldg(bias + o) : 0.f;
+#pragma unroll 1
+                    for (int cc = 0; cc < kTileN / 16; ++cc) {
+                        uint32_t v[16];
+                        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + b * 256 + mt * 128 + cc * 16, v);
+                        tmem_ld_wait();
+                        const long long P0 = pt * kTileN + cc * 16;
+                        if (!o_ok || P0 >= g.P) continue;
+                        uint32_t n0, opos0;
+                        g.d_ov.divmod((uint32_t)P0, n0, opos0);
+                        float* dst = y + ((size_t)n0 * g.O + o) * g.ov + opos0;
+                        const bool fast = (opos0 + 16 <= (uint32_t)g.ov) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                        if (fast) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    float offv[D];
+                            for (int i = 0; i < 4; ++i) {
+                                const float4 val = make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
+                                                               __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
+                                if (KS == 1) *reinterpret_cast<float4*>(dst + 4 * i) = val;
+                                else atomicAdd(reinterpret_cast<float4*>(dst + 4 * i), val);
+                            }
+                        } else {
 #pragma unroll
-                    for (int a = 0; a < D; ++a)
-                        offv[a] = (DEFORM && key >= 0 && cur.pok[i]) ? src[(size_t)(sl * D + a) * 128 + ctid + 64 * i] : 0.f;
-                    fill_entry_from<D, DEFORM>(g, offv, cur.op[i], cur.pok[i], key,
-                                               tab + ((size_t)tb * max_slots + sl) * 128 + ctid + 64 * i);
+                            for (int i = 0; i < 16; ++i) {
+                                const long long P = P0 + i;
+                                if (P < g.P) {
+                                    uint32_t n, opos;
+                                    g.d_ov.divmod((uint32_t)P, n, opos);
+                                    float* d1 = y + ((size_t)n * g.O + o) * g.ov + opos;
+                                    if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
+                                    else atomicAdd(d1, __uint_as_float(v[i]) + bv);
+                                }
+                            }
+                        }
+                    }
                 }
+                tc_fence_before();
+                mbar_arrive_warp(&ctl->acc_empty[b]);
+                et += gridDim.x;
+                ++etl;
+                PROF_ADD(0)
+                continue;
             }
-            mbar_arrive_warp(&ctl->tab_full[tb]);
-            advance(cur);
-            ++it;
-            rt.next(n_tabs);
+            if (tab_free) {
+                PROF_T0
+                waiting = false;
+                cp_async_wait<1>();             // this stage's offsets have landed; the next stage's may be in flight
+                const uint32_t tb = rt.i;
+                const SlotInfo si = stage_slots(cur);
+                if (lane < 8) ctl->slot_of_chunk[tb][lane] = si.my_slot;
+                const float* src = my_ost + (size_t)(it & 1u) * max_slots * D * 128;
+                for (int sl = 0; sl < si.nslots; ++sl) {
+                    const int key = slot_key(si, sl);
+#pragma unroll
+                    for (int i = 0; i < CR; ++i) {
+                        const long long P = cur.pt * kTileN + lane + 32 * i;
+                        const bool pok = P < g.P;
+                        const OutPos op = decompose_pos(g, pok ? P : 0);
+                        float offv[D];
+#pragma unroll
+                        for (int a = 0; a < D; ++a)
+                            offv[a] = (DEFORM && key >= 0 && pok) ? src[(size_t)(sl * D + a) * 128 + lane + 32 * i] : 0.f;
+                        fill_entry_from<D, DEFORM>(g, offv, op, pok, key, tab + ((size_t)tb * max_slots + sl) * 128 + lane + 32 * i);
+                    }
+                }
+                mbar_arrive_warp(&ctl->tab_full[tb]);
+                skip(cur, kFwdCoordWarps);
+                for (int i = 0; i < kFwdCoordWarps; ++i) rt.next(n_tabs);
+                {
+                    Cur pre = cur;              // the stage after the next one goes into the buffer just read
+                    skip(pre, kFwdCoordWarps);
+                    prefetch(pre, it & 1u);
+                }
+                ++it;
+                PROF_ADD(1)
+                continue;
+            }
+            // nothing to do yet: bounded wait for either event
+            if (!waiting) {
+                waiting = true;
+                t0 = clock64();
+            } else if (clock64() - t0 > kWaitCycles) {
+                atomicOr(&g_tc_status, 1u);
+                break;
+            }
         }
         cp_async_wait<0>();
-    } else if (warp < 2 + kCoordWarps + GW) {
+        PROF_OUT(1, warp == 2 && lane == 0)
+    } else {
         // ------------------------------------------------ gather warps
-        // A stage is produced in passes of RPP rows per thread; the loads of the next pass are in flight while
-        // the current pass is interpolated and stored, across stage and tile boundaries.
-        const int gtid = threadIdx.x - 32 * (2 + kCoordWarps);   // 0..255
+        // Within a thread a stage is produced in passes of RPP rows; where the registers allow it the loads
+        // of the next pass are in flight while the current one is interpolated and stored.
+        const int gtid = threadIdx.x - 32 * (2 + kFwdCoordWarps);   // 0..GW*32-1
         const int chunk = gtid % 8;                 // 16-byte chunk of the 128-byte row
         const int row0 = gtid / 8;                  // rows row0 + RS*i, i = 0..RT-1
         constexpr int NQ = DEFORM ? (1 << D) : 1;
-        constexpr int RT = 128 * 8 / (GW * 32);                    // rows per thread and stage: 4 or 2
-        constexpr int RS = GW * 4;                                 // row stride between a thread's rows
-        constexpr int RPP = (GW == 16) ? RT : RT / 2;              // rows per pass (one row per pass: +31 % time)
-        constexpr int PPS = RT / RPP;                              // passes per stage
-        // 2-D: the next pass is issued before the current one is finished (16 loads in flight);
-        // 3-D: one pass at a time already has 16 loads in flight, and two would not fit the register file.
-        constexpr bool kOverlap = (D == 2 || !DEFORM) && GW == 8;
+        constexpr int RT = 128 * 8 / (GW * 32);     // rows per thread and stage
+        constexpr int RS = GW * 4;                  // row stride between a thread's rows
+        constexpr int RPP = (RT >= 2 && !(D == 3 && DEFORM && GW > 8)) ? 2 : 1;   // rows per pass (16 or 8 loads)
+        constexpr int PPS = RT / RPP;               // passes per stage
+        // 2-D: two passes in flight (16 loads); 3-D: one pass already has 16 loads in flight, and two would
+        // not fit the register file.
+        constexpr bool kOverlap = (D == 2 || !DEFORM) && PPS >= 2 && GW <= 10;
         struct Pass {
             uint4 q[RPP][NQ];
             float w[RPP][NQ];
             uint32_t s, ph;     // operand stage of this pass and the phase of its barriers
             int h;
         };
-        // issue cursor
-        long long ct = blockIdx.x;
+        // issue cursor: stage sequence (tile, K chunk) of this CTA
+        long long ct = blockIdx.x, cpt = 0;
         int ckc = 0, ckc_end = 0, ch = 0, cj = 0, cc = 0, csl = 0;
         Ring rtab, rstg;            // table buffer and operand stage of the issue cursor
-        size_t nbase[RT];
         bool failed = false;
+        PROF_DECL
         auto init_tile = [&]() {
             const int ks = (int)(ct % KS);
             const long long tt = ct / KS;
-            const long long pt = tt % PT;
+            cpt = tt % PT;
             cj = (int)(tt / PT / MB);
             ckc = ks * cpk;
             ckc_end = (ckc + cpk < KC) ? ckc + cpk : KC;
-#pragma unroll
-            for (int i = 0; i < RT; ++i) {
-                const long long P = pt * kTileN + row0 + RS * i;
-                uint32_t n = 0, opos = 0;
-                if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
-                nbase[i] = (size_t)n * g.iv * g.C;
+        };
+        auto next_stage = [&]() {
+            rtab.next(n_tabs);
+            rstg.next(n_stages);
+            if (++ckc == ckc_end) {
+                ct += gridDim.x;
+                if (ct < n_tiles) init_tile();
             }
         };
         if (ct < n_tiles) init_tile();
@@ -274,7 +389,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             if (ct >= n_tiles || failed) return false;
             const uint32_t tb = rtab.i;
             if (ch == 0) {
-                if (!mbar_wait(&ctl->tab_full[tb], rtab.ph)) { failed = true; return false; }
+                { PROF_T0 const bool okw = mbar_wait(&ctl->tab_full[tb], rtab.ph); PROF_ADD(0) if (!okw) { failed = true; return false; } }
                 csl = ctl->slot_of_chunk[tb][chunk];
                 const int kp = ckc * kTileK + chunk * 8;
                 uint32_t tap, cl;
@@ -284,13 +399,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             const Entry* trow = tab + ((size_t)tb * max_slots + csl) * 128;
 #pragma unroll
             for (int r = 0; r < RPP; ++r) {
-#pragma unroll
-                for (int hh = 0; hh < PPS; ++hh) {
-                    if (hh == ch) {
-                        const int i = hh * RPP + r;
-                        gather_issue_w<D, DEFORM>(trow + row0 + RS * i, xcl + nbase[i] + cc, g.C, p.q[r], p.w[r]);
-                    }
-                }
+                const int row = row0 + RS * (ch * RPP + r);
+                const long long P = cpt * kTileN + row;
+                uint32_t n = 0;
+                if (P < g.P) n = g.d_ov.div((uint32_t)P);
+                gather_issue_w<D, DEFORM>(trow + row, xcl + (size_t)n * g.iv * g.C + cc, g.C, p.q[r], p.w[r]);
             }
             p.s = rstg.i;
             p.ph = rstg.ph;
@@ -298,19 +411,14 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             if (ch == PPS - 1) mbar_arrive_warp(&ctl->tab_empty[tb]);   // this warp is done with the stage's table
             if (++ch == PPS) {
                 ch = 0;
-                rtab.next(n_tabs);
-                rstg.next(n_stages);
-                if (++ckc == ckc_end) {
-                    ct += gridDim.x;
-                    if (ct < n_tiles) init_tile();
-                }
+                next_stage();
             }
             return true;
         };
         auto finish = [&](Pass& p) -> bool {
             const uint32_t s = p.s;
             if (p.h == 0) {
-                if (!mbar_wait(&ctl->empty[s], p.ph ^ 1u)) { failed = true; return false; }
+                { PROF_T0 const bool okw = mbar_wait(&ctl->empty[s], p.ph ^ 1u); PROF_ADD(1) if (!okw) { failed = true; return false; } }
             }
             const uint32_t b_base = smem_u32(smem + s * kFwdStageBytes + 2 * kTileBytes);
 #pragma unroll
@@ -340,64 +448,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 if (!finish(pa)) break;
             }
         }
-    } else {
-        // ------------------------------------------------ epilogue
-        const int q = warp & 3;                     // tensor-memory lane quarter this warp may access
-        uint32_t tl = 0;
-        bool ok = true;
-        for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
-            const int ks = (int)(t % KS);
-            const long long tt = t / KS;
-            const long long pt = tt % PT;
-            const int mb = (int)((tt / PT) % MB);
-            const int j = (int)(tt / PT / MB);
-            const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
-            const uint32_t b = tl & 1;
-            ok = mbar_wait(&ctl->acc_full[b], (tl >> 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-            for (int mt = 0; mt < mtb; ++mt) {
-                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;      // output channel within the group
-                const bool o_ok = ol < g.Og;
-                const int o = j * g.Og + ol;
-                const float bv = (bias != nullptr && o_ok && ks == 0) ? __ldg(bias + o) : 0.f;
-#pragma unroll 1
-                for (int cc = 0; cc < kTileN / 32; ++cc) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + b * 256 + mt * 128 + cc * 32, v);
-                    tmem_ld_wait();
-                    const long long P0 = pt * kTileN + cc * 32;
-                    if (!o_ok || P0 >= g.P) continue;
-                    uint32_t n0, opos0;
-                    g.d_ov.divmod((uint32_t)P0, n0, opos0);
-                    float* dst = y + ((size_t)n0 * g.O + o) * g.ov + opos0;
-                    const bool fast = (opos0 + 32 <= (uint32_t)g.ov) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                    if (fast) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float4 val = make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
-                                                           __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
-                            if (KS == 1) *reinterpret_cast<float4*>(dst + 4 * i) = val;
-                            else atomicAdd(reinterpret_cast<float4*>(dst + 4 * i), val);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const long long P = P0 + i;
-                            if (P < g.P) {
-                                uint32_t n, opos;
-                                g.d_ov.divmod((uint32_t)P, n, opos);
-                                float* d1 = y + ((size_t)n * g.O + o) * g.ov + opos;
-                                if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
-                                else atomicAdd(d1, __uint_as_float(v[i]) + bv);
-                            }
-                        }
-                    }
-                }
-            }
-            tc_fence_before();
-            mbar_arrive_warp(&ctl->acc_empty[b]);
-        }
+        PROF_OUT(2, gtid == 0)
     }
 
     // teardown: every role has left its loop (normally or after a bounded wait gave up)
@@ -438,18 +489,22 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     const TcDims d = tc_dims(g);
     const int max_slots = max_slots_per_chunk(g, 8);
     const size_t tab_one = (size_t)max_slots * 128 * sizeof(TabEntry<D, DEFORM>);
-    const size_t ost_bytes = (size_t)kOffRing * max_slots * D * 128 * sizeof(float);
-    int n_tabs = kMaxTabs;
-    size_t fixed = n_tabs * tab_one + ost_bytes + sizeof(FwdCtl) + 1024;
-    if ((kSmemLimit - (long long)fixed) / kFwdStageBytes < kMaxStages) {       // big tables: two buffers instead of three
-        n_tabs = 2;
-        fixed = n_tabs * tab_one + ost_bytes + sizeof(FwdCtl) + 1024;
+    const size_t ost_bytes = (size_t)kFwdOffRing * max_slots * D * 128 * sizeof(float);
+    auto need = [&](int stages, int tabs) {
+        return (long long)stages * kFwdStageBytes + (long long)tabs * tab_one + ost_bytes + sizeof(FwdCtl) + 1024;
+    };
+    // The four coordinate warps work on four tables at once and wait on the barriers of a table buffer by phase
+    // parity, which is only sound while no warp runs two laps of the ring ahead of another: with the tables
+    // consumed in order that holds for rings of four and more.  A ring of five or six comes before the fourth
+    // operand stage (the stage count hardly matters: the producers, not the MMA, bound a stage).
+    int stages = 0, n_tabs = 0;
+    const int pref[][2] = {{4, 6}, {4, 5}, {3, 6}, {3, 5}, {4, 4}, {3, 4}, {2, 6}, {2, 5}, {2, 4}};
+    for (const auto& c : pref) {
+        if (need(c[0], c[1]) <= kSmemLimit) { stages = c[0]; n_tabs = c[1]; break; }
     }
-    int stages = (int)((kSmemLimit - (long long)fixed) / kFwdStageBytes);
-    if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 3) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
-    const int smem = (int)(fixed + (size_t)stages * kFwdStageBytes);
-    constexpr int GW = 8;      // 16 gather warps (2 rows each) measured slower on the 2-D benchmark shape
+    if (stages == 0) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
+    const int smem = (int)need(stages, n_tabs);
+    constexpr int GW = 16;
     auto kern = tc_forward_kernel<D, DEFORM, GW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     // split the K range when there are fewer tiles than SMs (small batches / late layers of a network)
