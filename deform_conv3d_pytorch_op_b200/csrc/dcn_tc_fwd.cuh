@@ -34,14 +34,10 @@ __device__ unsigned long long g_fwd_prof[32];
 
 constexpr int kMaxStages = 4;
 constexpr int kFwdCoordWarps = 4;               // forward: coordinate + epilogue warps, one per tensor-memory lane quarter
-constexpr int kCoordWarps = 2;
-constexpr int kGatherWarps = 8;
 constexpr int fwd_threads(int gw) { return 32 * (2 + kFwdCoordWarps + gw); }
 constexpr int kFwdStageBytes = 3 * kTileBytes;      // A0 | A1 | B
 constexpr int kSmemLimit = 232448;                   // 227 KB opt-in maximum per CTA
 
-constexpr int kMaxTabs = 3;          // weight-gradient kernel: table ring
-constexpr int kOffRing = 3;          // weight-gradient kernel: offset prefetch distance of the coordinate warps + 1
 constexpr int kFwdMaxTabs = 6;
 constexpr int kFwdOffRing = 2 * kFwdCoordWarps;   // two private offset staging buffers per coordinate warp
 

@@ -7,15 +7,20 @@
 // the position range; partial sums are added to dW with fp32 atomics (dW is tiny and L2-resident).
 //   A operand: dy, bf16, pre-packed by pack_dy into swizzled [128 o][64 P] tiles  -> K-major, bulk-copied
 //   B operand: sampled patch, [64 P rows][64 k' per 128-byte row] sub-tiles        -> MN-major, produced here
-// Warps: 0 MMA issue, 1 dy-tile loader, 2-3 coordinate warps, 4-11 gather warps (dcn_tc_sampler.cuh),
-// 12-15 epilogue.  The k' block of a CTA is fixed, so the (deformable group, tap) key of every chunk column and
-// the slot numbering are computed once.
+// Warps: 0 MMA issue, 1 dy-tile loader, 2-5 coordinate warps (warp k fills the table of every 4th stage, as in
+// dcn_tc_fwd.cuh; after the last table the same warps are the epilogue), 6-21 gather warps (dcn_tc_sampler.cuh).
+// The k' block of a CTA is fixed, so the (deformable group, tap) key of every chunk column and the slot
+// numbering are computed once.
 #pragma once
 
-constexpr int kWg2Threads = 32 * (2 + kCoordWarps + kGatherWarps + kEpilogueWarps);
+constexpr int kWgCoordWarps = 4;
+constexpr int kWgGatherWarps = 16;
+constexpr int kWgMaxTabs = 6;
+constexpr int kWgOffRing = 2 * kWgCoordWarps;       // two private offset staging buffers per coordinate warp
+constexpr int kWg2Threads = 32 * (2 + kWgCoordWarps + kWgGatherWarps);
 
 struct Wg2Ctl {
-    uint64_t full[kMaxStages], empty[kMaxStages], acc_full, tab_full[kMaxTabs], tab_empty[kMaxTabs];
+    uint64_t full[kMaxStages], empty[kMaxStages], acc_full, tab_full[kWgMaxTabs], tab_empty[kWgMaxTabs];
     uint32_t tmem_base;
     int slot_of_chunk[32];
     int key_of_slot[32];
@@ -34,8 +39,8 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
     const int stage_bytes = a_tiles * kTileBytes + 4 * 8192;          // A tiles | B (4 sub-tiles of 8 KB)
     Entry* tab = reinterpret_cast<Entry*>(smem + (size_t)n_stages * stage_bytes);        // [n_tabs][max_slots][64]
     float* ostage = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(tab) +
-                                             (size_t)n_tabs * max_slots * 64 * sizeof(Entry));   // [3][max_slots][D][64]
-    Wg2Ctl* ctl = reinterpret_cast<Wg2Ctl*>(ostage + (size_t)kOffRing * max_slots * D * 64);
+                                             (size_t)n_tabs * max_slots * 64 * sizeof(Entry));   // [kWgOffRing][max_slots][D][64]
+    Wg2Ctl* ctl = reinterpret_cast<Wg2Ctl*>(ostage + (size_t)kWgOffRing * max_slots * D * 64);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
@@ -50,13 +55,13 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl->full[s], kGatherWarps + 1);
+            mbar_init(&ctl->full[s], kWgGatherWarps + 1);
             mbar_init(&ctl->empty[s], 1);
         }
         mbar_init(&ctl->acc_full, 1);
-        for (int b = 0; b < kMaxTabs; ++b) {
-            mbar_init(&ctl->tab_full[b], kCoordWarps);
-            mbar_init(&ctl->tab_empty[b], kGatherWarps);
+        for (int b = 0; b < kWgMaxTabs; ++b) {
+            mbar_init(&ctl->tab_full[b], 1);                  // the coordinate warp that filled it
+            mbar_init(&ctl->tab_empty[b], kWgGatherWarps);
         }
         fence_barrier_init();
     }
@@ -121,15 +126,22 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 }
             }
         }
-    } else if (warp < 2 + kCoordWarps) {
-        // ------------------------------------------------ coordinate warps: thread = position row of the chunk
-        const int row = threadIdx.x - 64;               // 0..63
-        auto prefetch = [&](int itp) {
+    } else if (warp < 2 + kWgCoordWarps) {
+        // ------------------------------------------------ coordinate warps, then epilogue
+        // Warp cw fills the tables of chunks cw, cw + 4, ...; a thread owns position rows lane and lane + 32.  The
+        // offsets of a chunk are fetched (4-byte cp.async) into one of the warp's two staging buffers while the
+        // warp's previous chunk is being filled.
+        const int cw = warp - 2;
+        float* my_ost = ostage + (size_t)cw * 2 * max_slots * D * 64;
+        auto prefetch = [&](int itp, uint32_t buf) {
             if (DEFORM && itp < n_chunks) {
-                const long long P = (c_begin + itp) * 64 + row;
-                if (P < g.P) {
+                float* dst = my_ost + (size_t)buf * max_slots * D * 64;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int row = lane + 32 * i;
+                    const long long P = (c_begin + itp) * 64 + row;
+                    if (P >= g.P) continue;
                     const OutPos op = decompose_pos(g, P);
-                    float* dst = ostage + (size_t)(itp % kOffRing) * max_slots * D * 64;
                     for (int sl = 0; sl < nslots; ++sl) {
                         const int key = ctl->key_of_slot[sl];
                         if (key < 0) continue;
@@ -142,39 +154,73 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             }
             cp_async_commit();
         };
-        prefetch(0);
-        prefetch(1);
+        prefetch(cw, 0);
+        prefetch(cw + kWgCoordWarps, 1);
         bool ok = true;
         Ring rt;
-        for (int it = 0; it < n_chunks && ok; ++it, rt.next(n_tabs)) {
-            prefetch(it + 2);
-            cp_async_wait<2>();
+        for (int i = 0; i < cw; ++i) rt.next(n_tabs);
+        uint32_t k = 0;
+        for (int it = cw; it < n_chunks && ok; it += kWgCoordWarps, ++k) {
             const uint32_t tb = rt.i;
-            const long long P = (c_begin + it) * 64 + row;
-            const bool pok = P < g.P;
-            const OutPos op = decompose_pos(g, pok ? P : 0);
             ok = mbar_wait(&ctl->tab_empty[tb], rt.ph ^ 1u);
             if (!ok) break;
-            const float* src = ostage + (size_t)(it % kOffRing) * max_slots * D * 64;
-            for (int sl = 0; sl < nslots; ++sl) {
-                const int key = ctl->key_of_slot[sl];
-                float offv[D];
+            cp_async_wait<1>();             // this chunk's offsets have landed; the next chunk's may be in flight
+            const float* src = my_ost + (size_t)(k & 1u) * max_slots * D * 64;
 #pragma unroll
-                for (int a = 0; a < D; ++a) offv[a] = (DEFORM && key >= 0 && pok) ? src[(size_t)(sl * D + a) * 64 + row] : 0.f;
-                fill_entry_from<D, DEFORM>(g, offv, op, pok, key, tab + ((size_t)tb * max_slots + sl) * 64 + row);
+            for (int i = 0; i < 2; ++i) {
+                const int row = lane + 32 * i;
+                const long long P = (c_begin + it) * 64 + row;
+                const bool pok = P < g.P;
+                const OutPos op = decompose_pos(g, pok ? P : 0);
+                for (int sl = 0; sl < nslots; ++sl) {
+                    const int key = ctl->key_of_slot[sl];
+                    float offv[D];
+#pragma unroll
+                    for (int a = 0; a < D; ++a) offv[a] = (DEFORM && key >= 0 && pok) ? src[(size_t)(sl * D + a) * 64 + row] : 0.f;
+                    fill_entry_from<D, DEFORM>(g, offv, op, pok, key, tab + ((size_t)tb * max_slots + sl) * 64 + row);
+                }
             }
             mbar_arrive_warp(&ctl->tab_full[tb]);
+            prefetch(it + 2 * kWgCoordWarps, k & 1u);      // into the buffer just read
+            for (int i = 0; i < kWgCoordWarps; ++i) rt.next(n_tabs);
         }
         cp_async_wait<0>();
-    } else if (warp < 2 + kCoordWarps + kGatherWarps) {
+        // ------------------------------------------------ epilogue: partial dW of this CTA -> atomics
+        const int q = warp & 3;
+        if (ok && n_chunks > 0 && mbar_wait(&ctl->acc_full, 0)) {
+            tc_fence_after();
+            for (int mt = 0; mt < mtb; ++mt) {
+                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
+                const bool o_ok = ol < g.Og;
+                float* dwo = dw + (size_t)(j * g.Og + (o_ok ? ol : 0)) * g.Cg * g.kv;
+                for (int cc = 0; cc < NW / 16; ++cc) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 16, v);
+                    tmem_ld_wait();
+                    if (!o_ok) continue;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int kq = nb * kWgNMax + cc * 16 + i;
+                        if (kq < g.kv * g.Cg) {
+                            uint32_t tp, cq;
+                            g.d_Cg.divmod((uint32_t)kq, tp, cq);
+                            atomicAdd(dwo + (size_t)cq * g.kv + tp, __uint_as_float(v[i]));
+                        }
+                    }
+                }
+            }
+        }
+    } else {
         // ------------------------------------------------ gather warps
-        const int gtid = threadIdx.x - 32 * (2 + kCoordWarps);   // 0..255
+        const int gtid = threadIdx.x - 32 * (2 + kWgCoordWarps);  // 0..511
         const int cj = gtid % 32;                   // chunk column (8 channels) inside the k' block
-        const int row0 = gtid / 32;                 // rows row0 + 8*i, i = 0..7
+        const int row0 = gtid / 32;                 // rows row0 + RS*i, i = 0..RT-1
         constexpr int NQ = DEFORM ? (1 << D) : 1;
-        constexpr int RPP = 2;                                     // rows per pass
-        constexpr int PPS = 8 / RPP;                               // passes per stage
-        constexpr bool kOverlap = (D == 2 || !DEFORM);             // see dcn_tc_fwd.cuh
+        constexpr int RS = kWgGatherWarps;                         // row stride between a thread's rows
+        constexpr int RT = 64 / RS;                                // rows per thread and stage
+        constexpr int RPP = (D == 3 && DEFORM) ? 1 : 2;            // rows per pass: 8 loads in flight
+        constexpr int PPS = RT / RPP;                              // passes per stage
+        constexpr bool kOverlap = false;                           // one pass at a time: 80 registers per thread
         const bool col_ok = cj * 8 < NW;
         int tap_, cch;
         chunk_key(g, j, nb * kWgNMax + cj * 8, tap_, cch);
@@ -198,7 +244,7 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             const Entry* trow = tab + ((size_t)tb * max_slots + sl) * 64;
 #pragma unroll
             for (int r = 0; r < RPP; ++r) {
-                const int row = row0 + 8 * (ch * RPP + r);
+                const int row = row0 + RS * (ch * RPP + r);
                 const long long P = (c_begin + cit) * 64 + row;
                 uint32_t n = 0, opos = 0;
                 if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
@@ -226,7 +272,7 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
 #pragma unroll
                 for (int r = 0; r < RPP; ++r) {
                     const uint4 v = gather_finish_w<D, DEFORM>(p.q[r], p.w[r]);
-                    st_shared_v4(b_base + swz_offset(row0 + 8 * (p.h * RPP + r), cj % 8), v.x, v.y, v.z, v.w);
+                    st_shared_v4(b_base + swz_offset(row0 + RS * (p.h * RPP + r), cj % 8), v.x, v.y, v.z, v.w);
                 }
             }
             if (p.h == PPS - 1) {
@@ -251,31 +297,6 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 if (!finish(pa)) break;
             }
         }
-    } else {
-        const int q = warp & 3;
-        if (n_chunks > 0 && mbar_wait(&ctl->acc_full, 0)) {
-            tc_fence_after();
-            for (int mt = 0; mt < mtb; ++mt) {
-                const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
-                const bool o_ok = ol < g.Og;
-                float* dwo = dw + (size_t)(j * g.Og + (o_ok ? ol : 0)) * g.Cg * g.kv;
-                for (int cc = 0; cc < NW / 32; ++cc) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 32, v);
-                    tmem_ld_wait();
-                    if (!o_ok) continue;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int kq = nb * kWgNMax + cc * 32 + i;
-                        if (kq < g.kv * g.Cg) {
-                            uint32_t tp, cq;
-                            g.d_Cg.divmod((uint32_t)kq, tp, cq);
-                            atomicAdd(dwo + (size_t)cq * g.kv + tp, __uint_as_float(v[i]));
-                        }
-                    }
-                }
-            }
-        }
     }
 
     tc_fence_before();
@@ -297,17 +318,18 @@ int launch_tc_wgrad(const Geom& g, const __nv_bfloat16* xcl, const float* off, c
     const int stage_bytes = a_tiles * kTileBytes + 4 * 8192;
     const int max_slots = max_slots_per_block(g);
     const size_t tab_one = (size_t)max_slots * 64 * sizeof(TabEntry<D, DEFORM>);
-    const size_t ost_bytes = (size_t)kOffRing * max_slots * D * 64 * sizeof(float);
-    int n_tabs = kMaxTabs;
-    size_t fixed = n_tabs * tab_one + ost_bytes + sizeof(Wg2Ctl) + 1024;
-    if ((kSmemLimit - (long long)fixed) / stage_bytes < 3) {
-        n_tabs = 2;
-        fixed = n_tabs * tab_one + ost_bytes + sizeof(Wg2Ctl) + 1024;
+    const size_t ost_bytes = (size_t)kWgOffRing * max_slots * D * 64 * sizeof(float);
+    auto need = [&](int stages, int tabs) {
+        return (long long)stages * stage_bytes + (long long)tabs * tab_one + ost_bytes + sizeof(Wg2Ctl) + 1024;
+    };
+    // table ring of at least four (see launch_tc_forward), preferably deeper than the four coordinate warps
+    int stages = 0, n_tabs = 0;
+    const int pref[][2] = {{3, 6}, {3, 5}, {2, 6}, {2, 5}, {3, 4}, {2, 4}};
+    for (const auto& c : pref) {
+        if (need(c[0], c[1]) <= kSmemLimit) { stages = c[0]; n_tabs = c[1]; break; }
     }
-    int stages = (int)((kSmemLimit - (long long)fixed) / stage_bytes);
-    if (stages > kMaxStages) stages = kMaxStages;
-    if (stages < 2 || max_slots > 32) return launch_tc_wgrad_direct<D, DEFORM>(g, xcl, off, dpk, dw, st);
-    const int smem = (int)(fixed + (size_t)stages * stage_bytes);
+    if (stages == 0 || max_slots > 32) return launch_tc_wgrad_direct<D, DEFORM>(g, xcl, off, dpk, dw, st);
+    const int smem = (int)need(stages, n_tabs);
     auto kern = tc_wgrad_kernel<D, DEFORM>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     dim3 grid((unsigned)(g.G * d.MB * d.NB), (unsigned)d.splits);
