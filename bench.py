@@ -249,8 +249,9 @@ def run_model(args):
                        "stock_layers": "channels_last_3d" if chl else "NCDHW",
                        "l2": "activations of one step exceed the 126 MB L2"},
             "roofline": None, "cpu_baseline": None, "e2e": e2e, "clocks": clocks,
-            # 8 deformable layers x (3 + 5 + 3) library launches per step (the other layers are cuDNN / torch)
-            "gpu_launches": n_deform * 11 * args.steps,
+            # 8 deformable layers x (3 forward + 7 fused backward) library launches per step (the other layers are
+            # cuDNN / torch)
+            "gpu_launches": n_deform * 10 * args.steps,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -128,7 +128,7 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
 int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
     if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_BACKWARD ? 2 : 1;
-    if (pass == DCN_PASS_BACKWARD) return 6;      // channels-last copy, dy pack, weight pack, dgrad, dx transpose, wgrad
+    if (pass == DCN_PASS_BACKWARD) return 7;      // channels-last copy, dy pack, weight pack, dgrad, dx transpose, wgrad, dW unpack
     Geom g;
     make_geom(p, g);
     return dcn::tc_launch_count(g, p->ndim, pass);

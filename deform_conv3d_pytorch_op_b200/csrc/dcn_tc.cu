@@ -179,19 +179,20 @@ int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cuda
 #include "dcn_tc_dgrad2.cuh"
 
 struct BwdWeightWorkspace {
-    size_t xcl_off, dpk_off, total;
+    size_t xcl_off, dpk_off, dwpk_off, total;
 };
 BwdWeightWorkspace bwd_weight_workspace(const Geom& g) {
     const WgDims d = wg_dims(g);
     BwdWeightWorkspace w;
     w.xcl_off = 0;
     w.dpk_off = align_up((size_t)g.N * g.iv * g.C * 2, 256);
-    w.total = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC * kTileBytes, 256);
+    w.dwpk_off = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC * kTileBytes, 256);
+    w.total = w.dwpk_off + align_up(dwpk_bytes(g), 256);
     return w;
 }
 
 struct BwdDataWorkspace {
-    size_t xcl_off, dpk_off, wpk_off, dxcl_off, dxcl_bytes, total;
+    size_t xcl_off, dpk_off, wpk_off, dxcl_off, dxcl_bytes, dwpk_off, total;      // dwpk: fused backward only
 };
 BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     const DgDims d = dg_dims(g);
@@ -201,7 +202,8 @@ BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     w.wpk_off = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC2 * kTileBytes, 256);
     w.dxcl_off = w.wpk_off + align_up((size_t)g.G * d.NB * d.OC * 2 * kTileBytes, 256);
     w.dxcl_bytes = align_up((size_t)g.N * g.iv * g.C * 4, 256);
-    w.total = w.dxcl_off + w.dxcl_bytes;
+    w.dwpk_off = w.dxcl_off + w.dxcl_bytes;
+    w.total = w.dwpk_off + align_up(dwpk_bytes(g), 256);
     return w;
 }
 
@@ -226,7 +228,7 @@ int tc_launch_count(const Geom& g, int ndim, int pass) {
     (void)g; (void)ndim;
     if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
     if (pass == 1) return 5;      // channels-last copy, dy pack, weight pack, implicit GEMM + scatter, dx transpose-add
-    return 3;                     // channels-last copy, dy pack, implicit GEMM
+    return 4;                     // channels-last copy, dy pack, implicit GEMM, dW unpack
 }
 
 int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
@@ -295,10 +297,15 @@ int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, cons
     if (r != 0) return r;
     pack_dy<<<dim3((unsigned)d.PC, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC);
     if (cudaGetLastError() != cudaSuccess) return -5;
-    if (ndim == 2) return deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dw, st)
-                                 : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dw, st);
-    return deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dw, st)
-                  : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
+    float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
+    r = dwpk_clear(g, dwpk, st);
+    if (r != 0) return r;
+    if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dwpk, st)
+                              : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dwpk, st);
+    else r = deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dwpk, st)
+                    : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dwpk, st);
+    if (r != 0) return r;
+    return dwpk_fold<true>(g, dwpk, dw, st);         // this entry point accumulates into dW
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -349,12 +356,16 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         }
     }
     if (dw != nullptr) {
-        if (cudaMemsetAsync(dw, 0, (size_t)g.O * g.Cg * g.kv * sizeof(float), st) != cudaSuccess) return -5;
+        float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
+        r = dwpk_clear(g, dwpk, st);
+        if (r != 0) return r;
         // the weight kernel reads dy tiles with the same layout and stride (PC2 == wg_dims().PC)
-        if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dw, st)
-                                  : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dw, st);
-        else r = deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dw, st)
-                        : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dw, st);
+        if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dwpk, st)
+                                  : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dwpk, st);
+        else r = deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dwpk, st)
+                        : launch_tc_wgrad<3, false>(g, xcl, off, dpk, dwpk, st);
+        if (r != 0) return r;
+        r = dwpk_fold<false>(g, dwpk, dw, st);       // the fused entry point overwrites dW
         if (r != 0) return r;
     }
     return 0;

@@ -170,20 +170,20 @@ tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, cons
             for (int mt = 0; mt < mtb; ++mt) {
                 const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
                 const bool o_ok = ol < g.Og;
-                float* dwo = dw + (size_t)(j * g.Og + (o_ok ? ol : 0)) * g.Cg * g.kv;
+                // partial sums go to the packed scratch dwpk[G][MB*256 rows][NB*256 columns] as 16-byte reductions
+                float* dwo = dw + ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
                 for (int cc = 0; cc < NW / 32; ++cc) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 32, v);
                     tmem_ld_wait();
                     if (!o_ok) continue;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int kq = nb * kWgNMax + cc * 32 + i;
-                        if (kq < g.kv * g.Cg) {
-                            uint32_t tp, cq;
-                            g.d_Cg.divmod((uint32_t)kq, tp, cq);
-                            atomicAdd(dwo + (size_t)cq * g.kv + tp, __uint_as_float(v[i]));
-                        }
+                    for (int i = 0; i < 8; ++i) {
+                        const int kq = nb * kWgNMax + cc * 32 + 4 * i;
+                        if (kq < g.kv * g.Cg)
+                            atomicAdd(reinterpret_cast<float4*>(dwo + cc * 32 + 4 * i),
+                                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
                     }
                 }
             }
@@ -220,6 +220,42 @@ inline WgDims wg_dims(const Geom& g) {
     d.cps = (int)((d.PC + splits - 1) / splits);
     d.splits = (int)((d.PC + d.cps - 1) / d.cps);
     return d;
+}
+
+// dwpk[G][rows][cols] (k' = tap * Cg + c along the columns) -> dW [O][Cg][kv] of the reference layout;
+// ACC adds to dW (the separate weight-gradient entry point accumulates), else dW is overwritten.
+template <bool ACC>
+__global__ void __launch_bounds__(256)
+unpack_dw(const Geom g, const float* __restrict__ dwpk, float* __restrict__ dw, int rows, int cols) {
+    const long long total = (long long)g.O * g.Cg * g.kv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int tap = (int)(i % g.kv);
+        const long long oc = i / g.kv;
+        const int c = (int)(oc % g.Cg);
+        const int o = (int)(oc / g.Cg);
+        const int j = o / g.Og, ol = o - j * g.Og;
+        const float v = dwpk[((size_t)j * rows + ol) * cols + (size_t)tap * g.Cg + c];
+        if (ACC) dw[i] += v;
+        else dw[i] = v;
+    }
+}
+
+inline size_t dwpk_bytes(const Geom& g) {
+    const WgDims d = wg_dims(g);
+    return (size_t)g.G * d.MB * 256 * d.NB * kWgNMax * sizeof(float);
+}
+
+// Zero the packed scratch before the weight-gradient kernel, fold it into dW after it.
+inline int dwpk_clear(const Geom& g, float* dwpk, cudaStream_t st) {
+    return cudaMemsetAsync(dwpk, 0, dwpk_bytes(g), st) == cudaSuccess ? 0 : -5;
+}
+template <bool ACC>
+int dwpk_fold(const Geom& g, const float* dwpk, float* dw, cudaStream_t st) {
+    const WgDims d = wg_dims(g);
+    const long long total = (long long)g.O * g.Cg * g.kv;
+    const int blocks = (int)((total + 255) / 256 < 4 * sm_count() ? (total + 255) / 256 : 4 * sm_count());
+    unpack_dw<ACC><<<blocks, 256, 0, st>>>(g, dwpk, dw, d.MB * 256, d.NB * kWgNMax);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 template <int D, bool DEFORM>

@@ -4,7 +4,8 @@
 //
 // GEMM view: M = output channels (128-row tiles, up to two per CTA), N = a block of up to 256 k' columns,
 // K = output positions, 64 per pipeline stage.  One CTA owns one (group, o-block, k'-block) and a slice of
-// the position range; partial sums are added to dW with fp32 atomics (dW is tiny and L2-resident).
+// the position range; partial sums are added with 16-byte fp32 reductions to a packed, zero-filled scratch
+// dwpk[o][k'] (tiny and L2-resident) that unpack_dw folds into dW's [O][Cg][kv] layout afterwards.
 //   A operand: dy, bf16, pre-packed by pack_dy into swizzled [128 o][64 P] tiles  -> K-major, bulk-copied
 //   B operand: sampled patch, [64 P rows][64 k' per 128-byte row] sub-tiles        -> MN-major, produced here
 // Warps: 0 MMA issue, 1 dy-tile loader, 2-5 coordinate warps (warp k fills the table of every 4th stage, as in
@@ -192,20 +193,20 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             for (int mt = 0; mt < mtb; ++mt) {
                 const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
                 const bool o_ok = ol < g.Og;
-                float* dwo = dw + (size_t)(j * g.Og + (o_ok ? ol : 0)) * g.Cg * g.kv;
+                // partial sums go to the packed scratch dwpk[G][MB*256 rows][NB*256 columns] as 16-byte reductions
+                float* dwo = dw + ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
                 for (int cc = 0; cc < NW / 16; ++cc) {
                     uint32_t v[16];
                     tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 16, v);
                     tmem_ld_wait();
                     if (!o_ok) continue;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int kq = nb * kWgNMax + cc * 16 + i;
-                        if (kq < g.kv * g.Cg) {
-                            uint32_t tp, cq;
-                            g.d_Cg.divmod((uint32_t)kq, tp, cq);
-                            atomicAdd(dwo + (size_t)cq * g.kv + tp, __uint_as_float(v[i]));
-                        }
+                    for (int i = 0; i < 4; ++i) {
+                        const int kq = nb * kWgNMax + cc * 16 + 4 * i;
+                        if (kq < g.kv * g.Cg)
+                            atomicAdd(reinterpret_cast<float4*>(dwo + cc * 16 + 4 * i),
+                                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
                     }
                 }
             }
