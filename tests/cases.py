@@ -97,6 +97,9 @@ TC_CASES = [
     Case("tc3_groups", 3, 1, 64, 64, (4, 7, 7), (3, 3, 3), (1, 2, 2), (2, 2, 2), (2, 2, 2), 4, 8, offset_std=2.0,
          bias=True),
     Case("tc3_o512", 3, 2, 128, 512, (2, 4, 4), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 32, offset_std=1.0),
+    # four (deformable group, tap) keys per 64-channel chunk and more position tiles than SMs: the large corner
+    # tables leave two operand stages, and CTAs with a second tile drain an accumulator between tables
+    Case("tc2_cpg16_tiles", 2, 8, 64, 64, (50, 50), (3, 3), (1, 1), (1, 1), (1, 1), 1, 16, offset_std=2.5),
 ]
 
 # --- BASELINE configurations 1-4 ------------------------------------------------------------------------
