@@ -161,8 +161,8 @@ def run_model(args):
     torch.backends.cudnn.benchmark = True
     chl = not args.no_channels_last
     if chl:
-        # cuDNN's convolutions and batch-norms run natively in channels-last; the deformable operator takes its
-        # inputs through .contiguous() (NCDHW) at the two late stages, where the tensors are small
+        # cuDNN's convolutions and batch-norms run natively in channels-last, and the deformable operator takes and
+        # returns channels-last activations as they are (only the offset tensors are converted)
         model = model.to(memory_format=torch.channels_last_3d)
     use_graph = not args.no_graph
     use_ddp = world > 1 and not args.no_ddp and not use_graph     # the graphed step all-reduces flat buckets itself

@@ -31,6 +31,7 @@ class dcn_problem(ctypes.Structure):
         ("cpg", ctypes.c_int32),
         ("in_", ctypes.c_int32 * 3), ("k", ctypes.c_int32 * 3), ("stride", ctypes.c_int32 * 3),
         ("pad", ctypes.c_int32 * 3), ("dil", ctypes.c_int32 * 3),
+        ("channels_last", ctypes.c_int32),
     ]
 
 
@@ -102,7 +103,7 @@ def _triple(v, ndim: int, fill: int):
 def make_problem(ndim: int, dtype: torch.dtype, N: int, C: int, O: int, in_size: Sequence[int],
                  kernel: Sequence[int], stride, pad, dil, G: int, cpg: int, deformable: bool = True,
                  std_size_rule: bool = False, oob_offset_grad: bool = True,
-                 precision: int = PREC_EXACT) -> dcn_problem:
+                 precision: int = PREC_EXACT, channels_last: bool = False) -> dcn_problem:
     p = dcn_problem()
     p.ndim = ndim
     if dtype == torch.float32:
@@ -121,6 +122,7 @@ def make_problem(ndim: int, dtype: torch.dtype, N: int, C: int, O: int, in_size:
     p.stride[:] = _triple(stride, ndim, 1)
     p.pad[:] = _triple(pad, ndim, 0)
     p.dil[:] = _triple(dil, ndim, 1)
+    p.channels_last = 1 if channels_last else 0
     return p
 
 

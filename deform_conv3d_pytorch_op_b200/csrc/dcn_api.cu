@@ -21,6 +21,8 @@ int validate(const dcn_problem* p) {
     if (p->dtype != DCN_F32 && p->dtype != DCN_F64) return DCN_ERR_UNSUPPORTED;
     if (p->precision != DCN_PREC_EXACT && p->precision != DCN_PREC_BF16) return DCN_ERR_UNSUPPORTED;
     if (p->precision == DCN_PREC_BF16 && p->dtype != DCN_F32) return DCN_ERR_UNSUPPORTED;
+    if (p->channels_last != 0 && p->channels_last != 1) return DCN_ERR_UNSUPPORTED;
+    if (p->channels_last && p->precision != DCN_PREC_BF16) return DCN_ERR_UNSUPPORTED;   // the SIMT kernels are NCHW
     if (p->N < 1 || p->C < 1 || p->O < 1 || p->G < 1) return DCN_ERR_SHAPE;
     if (p->C % p->G != 0 || p->O % p->G != 0) return DCN_ERR_SHAPE;            // deform_conv3d_model.py:32-35
     if (p->deformable) {
@@ -56,6 +58,7 @@ void make_geom(const dcn_problem* p, Geom& g) {
     }
     g.Cg = g.C / g.G; g.Og = g.O / g.G; g.Kg = g.Cg * g.kv;
     g.oob = (p->ndim == 3 && p->deformable && p->oob_offset_grad) ? 1 : 0;
+    g.cl = p->channels_last ? 1 : 0;
     g.P = (long long)g.N * g.ov;
     g.d_ov.init(g.ov); g.d_ow.init(g.out[2]); g.d_oh.init(g.out[1]);
     g.d_kw.init(g.k[2]); g.d_kh.init(g.k[1]); g.d_kv.init(g.kv);
@@ -128,7 +131,7 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
 int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
     if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_BACKWARD ? 2 : 1;
-    if (pass == DCN_PASS_BACKWARD) return 7;      // channels-last copy, dy pack, weight pack, dgrad, dx transpose, wgrad, dW unpack
+    if (pass == DCN_PASS_BACKWARD) return p->channels_last ? 6 : 7;   // input copy, dy pack, weight pack, dgrad, (dx transpose,) wgrad, dW unpack
     Geom g;
     make_geom(p, g);
     return dcn::tc_launch_count(g, p->ndim, pass);
@@ -290,6 +293,7 @@ static dcn_problem make3d(int dtype, int N, int C, int L, int H, int W, int O, i
     p.pad[0] = pl; p.pad[1] = ph; p.pad[2] = pw;
     p.stride[0] = sl; p.stride[1] = sh; p.stride[2] = sw;
     p.dil[0] = dl; p.dil[1] = dh; p.dil[2] = dw;
+    p.channels_last = 0;
     return p;
 }
 static int legacy(int r) { return r == DCN_OK ? 1 : r; }

@@ -46,6 +46,7 @@ struct Geom {
     int iv, ov, kv;      // products of in / out / k
     int Cg, Og, Kg;      // per convolution group: input channels, output channels, Cg*kv
     int oob;             // 3-D: reference pull-back term for invalid samples in the offset gradient
+    int cl;              // x, y and their gradients are stored channels-last ([N, spatial, channels])
     long long P;         // N * ov  (flattened output positions)
     FastDiv d_ov, d_ow, d_oh, d_kw, d_kh, d_kv, d_Cg, d_cpg;
 };

@@ -441,6 +441,23 @@ bias_grad_kernel(const Geom g, const T* __restrict__ dy, T* __restrict__ dbias) 
     if (threadIdx.x == 0) dbias[o] = red[0];
 }
 
+// Same for a channels-last dy [N * ov positions][O]: a block sums one channel over all positions.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bias_grad_cl_kernel(const Geom g, const T* __restrict__ dy, T* __restrict__ dbias) {
+    __shared__ T red[kThreads];
+    const int o = blockIdx.x;
+    T s = (T)0;
+    for (long long P = threadIdx.x; P < g.P; P += kThreads) s += dy[(size_t)P * g.O + o];
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int st = kThreads / 2; st > 0; st >>= 1) {
+        if (threadIdx.x < st) red[threadIdx.x] += red[threadIdx.x + st];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dbias[o] = red[0];
+}
+
 template <typename T, int D>
 __global__ void debug_points_kernel(const Geom g, const T* __restrict__ off, int n, T* __restrict__ coords,
                                     int32_t* __restrict__ valid, int32_t* __restrict__ lo,
@@ -533,7 +550,8 @@ int simt_backward_weight(const Geom& g, int dtype, int ndim, int deform, const v
 }
 
 int bias_grad(const Geom& g, int dtype, const void* dy, void* dbias, cudaStream_t st) {
-    if (dtype == 0) bias_grad_kernel<float><<<g.O, kThreads, 0, st>>>(g, (const float*)dy, (float*)dbias);
+    if (g.cl) bias_grad_cl_kernel<float><<<g.O, kThreads, 0, st>>>(g, (const float*)dy, (float*)dbias);
+    else if (dtype == 0) bias_grad_kernel<float><<<g.O, kThreads, 0, st>>>(g, (const float*)dy, (float*)dbias);
     else bias_grad_kernel<double><<<g.O, kThreads, 0, st>>>(g, (const double*)dy, (double*)dbias);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

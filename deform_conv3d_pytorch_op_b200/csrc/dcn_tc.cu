@@ -167,7 +167,26 @@ FwdWorkspace fwd_workspace(const Geom& g) {
     return w;
 }
 
+// fp32 -> bf16 of an input that already is channels-last (8 elements per thread; C is a multiple of 8)
+__global__ void __launch_bounds__(256)
+cast_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ xcl, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(x) + 2 * i);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(x) + 2 * i + 1);
+        reinterpret_cast<uint4*>(xcl)[i] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w),
+                                                      pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+    }
+}
+
 int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cudaStream_t st) {
+    if (g.cl) {
+        if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return -7;      // vector loads
+        const size_t n8 = (size_t)g.N * g.iv * g.C / 8;
+        const size_t want = (n8 + 255) / 256;
+        const int blocks = (int)(want < (size_t)(8 * sm_count()) ? want : (size_t)(8 * sm_count()));
+        cast_bf16<<<blocks, 256, 0, st>>>(x, xcl, n8);
+        return cudaGetLastError() == cudaSuccess ? 0 : -5;
+    }
     dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
     to_channels_last_bf16<<<grid, 256, 0, st>>>(x, xcl, g.C, g.iv);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
@@ -225,9 +244,9 @@ size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
 }
 
 int tc_launch_count(const Geom& g, int ndim, int pass) {
-    (void)g; (void)ndim;
+    (void)ndim;
     if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
-    if (pass == 1) return 5;      // channels-last copy, dy pack, weight pack, implicit GEMM + scatter, dx transpose-add
+    if (pass == 1) return g.cl ? 4 : 5;   // input copy, dy pack, weight pack, implicit GEMM + scatter, (dx transpose-add)
     return 4;                     // channels-last copy, dy pack, implicit GEMM, dW unpack
 }
 
@@ -257,7 +276,9 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
     __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
     uint8_t* dpk = base + l.dpk_off;
     uint8_t* wpk = base + l.wpk_off;
-    float* dxcl = dx != nullptr ? reinterpret_cast<float*>(base + l.dxcl_off) : nullptr;
+    if (g.cl && dx != nullptr && (reinterpret_cast<uintptr_t>(dx) & 15) != 0) return -7;   // 16-byte reductions
+    // a channels-last dx is the scatter target itself (this entry point accumulates into dx)
+    float* dxcl = dx == nullptr ? nullptr : (g.cl ? dx : reinterpret_cast<float*>(base + l.dxcl_off));
     if (!deform) doff = nullptr;
     const DgDims d = dg_dims(g);
     int r = 0;
@@ -265,10 +286,11 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
         r = launch_channels_last(g, x, xcl, st);
         if (r != 0) return r;
     }
-    pack_dy<<<dim3((unsigned)d.PC2, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC2);
+    r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
+    if (r != 0) return r;
     pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
     if (cudaGetLastError() != cudaSuccess) return -5;
-    if (dxcl != nullptr && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
+    if (dxcl != nullptr && !g.cl && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
     if (doff != nullptr &&
         cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * ndim * g.ov * sizeof(float), st) != cudaSuccess)
         return -5;
@@ -277,7 +299,7 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
     else r = deform ? launch_tc_dgrad<3, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
                     : launch_tc_dgrad<3, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
     if (r != 0) return r;
-    if (dx != nullptr) {
+    if (dx != nullptr && !g.cl) {
         dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
         from_channels_last<true><<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
         if (cudaGetLastError() != cudaSuccess) return -5;
@@ -295,8 +317,8 @@ int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, cons
     const WgDims d = wg_dims(g);
     int r = launch_channels_last(g, x, xcl, st);
     if (r != 0) return r;
-    pack_dy<<<dim3((unsigned)d.PC, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    r = launch_pack_dy(g, dy, dpk, d.MT, d.PC, st);
+    if (r != 0) return r;
     float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
     r = dwpk_clear(g, dwpk, st);
     if (r != 0) return r;
@@ -324,7 +346,9 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
     const __nv_bfloat16* xcl = static_cast<const __nv_bfloat16*>(xcl_in);
     uint8_t* dpk = base + l.dpk_off;
     uint8_t* wpk = base + l.wpk_off;
-    float* dxcl = dx != nullptr ? reinterpret_cast<float*>(base + l.dxcl_off) : nullptr;
+    if (g.cl && dx != nullptr && (reinterpret_cast<uintptr_t>(dx) & 15) != 0) return -7;   // 16-byte reductions
+    // a channels-last dx is the scatter target itself (zero-filled here: this entry point overwrites)
+    float* dxcl = dx == nullptr ? nullptr : (g.cl ? dx : reinterpret_cast<float*>(base + l.dxcl_off));
     if (!deform) doff = nullptr;
     const DgDims d = dg_dims(g);
     int r = 0;
@@ -335,8 +359,8 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         if (r != 0) return r;
         xcl = mine;
     }
-    pack_dy<<<dim3((unsigned)d.PC2, (unsigned)(g.G * d.MT)), 256, 0, st>>>(g, dy, dpk, d.MT, d.PC2);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
+    if (r != 0) return r;
     if (dx != nullptr || doff != nullptr) {
         pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
         if (cudaGetLastError() != cudaSuccess) return -5;
@@ -349,7 +373,7 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         else r = deform ? launch_tc_dgrad<3, true>(g, xcl, off, dpk, wpk, dxcl, doff, st)
                         : launch_tc_dgrad<3, false>(g, xcl, off, dpk, wpk, dxcl, doff, st);
         if (r != 0) return r;
-        if (dx != nullptr) {
+        if (dx != nullptr && !g.cl) {
             dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
             from_channels_last<false><<<grid, 256, 0, st>>>(dxcl, dx, g.C, g.iv);
             if (cudaGetLastError() != cudaSuccess) return -5;

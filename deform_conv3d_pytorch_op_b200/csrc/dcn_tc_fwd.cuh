@@ -258,6 +258,18 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                         tmem_ld_wait();
                         const long long P0 = pt * kTileN + cc * 16;
                         if (!o_ok || P0 >= g.P) continue;
+                        if (g.cl) {
+                            // channels-last y: the 32 lanes of the warp hold 32 consecutive channels of a position
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                if (P0 + i < g.P) {
+                                    float* d1 = y + (size_t)(P0 + i) * g.O + o;
+                                    if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
+                                    else atomicAdd(d1, __uint_as_float(v[i]) + bv);
+                                }
+                            }
+                            continue;
+                        }
                         uint32_t n0, opos0;
                         g.d_ov.divmod((uint32_t)P0, n0, opos0);
                         float* dst = y + ((size_t)n0 * g.O + o) * g.ov + opos0;

@@ -49,6 +49,34 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
     }
 }
 
+// Same tiles from a channels-last dy [N * ov positions][O]: a thread packs 8 consecutive positions of one
+// output channel (one 16-byte chunk); consecutive threads take consecutive channels, so the reads coalesce.
+__global__ void __launch_bounds__(256)
+pack_dy_cl(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, int MT, long long PC) {
+    const long long pc = blockIdx.x;
+    const int mt = blockIdx.y % MT, j = blockIdx.y / MT;
+    uint8_t* dst = dpk + (((size_t)j * MT + mt) * PC + pc) * kTileBytes;
+    for (int item = threadIdx.x; item < 128 * 8; item += 256) {
+        const int row = item % 128, chunk = item / 128;
+        const int ol = mt * 128 + row;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const long long P = pc * 64 + chunk * 8 + e;
+            v[e] = (ol < g.Og && P < g.P) ? __ldg(dy + (size_t)P * g.O + j * g.Og + ol) : 0.f;
+        }
+        *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) =
+            make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+    }
+}
+
+inline int launch_pack_dy(const Geom& g, const float* dy, uint8_t* dpk, int MT, long long PC, cudaStream_t st) {
+    const dim3 grid((unsigned)PC, (unsigned)(g.G * MT));
+    if (g.cl) pack_dy_cl<<<grid, 256, 0, st>>>(g, dy, dpk, MT, PC);
+    else pack_dy<<<grid, 256, 0, st>>>(g, dy, dpk, MT, PC);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 template <int D, bool DEFORM>
 __global__ void __launch_bounds__(kWgThreads, 1)
 tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,

@@ -47,7 +47,8 @@ class Op:
 
     def __init__(self, x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, channel_per_group: int,
                  group: int, deformable: bool = True, std_size_rule: bool = False,
-                 oob_offset_grad: Optional[bool] = None, precision: Optional[str] = None):
+                 oob_offset_grad: Optional[bool] = None, precision: Optional[str] = None,
+                 channels_last: Optional[bool] = None):
         ndim = x.dim() - 2
         if ndim not in (2, 3):
             raise DcnError("input dim")                       # reference: check(input_dim == 5, "input dim")
@@ -62,9 +63,15 @@ class Op:
         if oob_offset_grad is None:
             oob_offset_grad = default_oob_offset_grad()
         cpg = channel_per_group if deformable else x.size(1)
+        # Channels-last activations (torch.channels_last / channels_last_3d storage) are taken and produced as they
+        # are by the bf16 path: no layout pass around the kernels.  Default: follow the input's memory format.
+        self.memory_format = torch.channels_last if ndim == 2 else torch.channels_last_3d
+        if channels_last is None:
+            channels_last = (not x.is_contiguous()) and x.is_contiguous(memory_format=self.memory_format)
         mk = lambda pr: _lib.make_problem(ndim, x.dtype, x.size(0), x.size(1), weight.size(0), tuple(x.shape[2:]),
                                           tuple(weight.shape[2:]), stride, padding, dilation, group, cpg,
-                                          deformable, std_size_rule, oob_offset_grad, pr)
+                                          deformable, std_size_rule, oob_offset_grad, pr,
+                                          channels_last and pr == _lib.PREC_BF16)
         if prec == "auto":
             # bf16 tensor-core path where the shape allows it and the problem is big enough to pay for its
             # layout pre-passes (eleven launches per step against three of the exact path)
@@ -86,6 +93,7 @@ class Op:
             raise DcnError("precision %r is not available for this problem (needs float32 tensors and channel "
                            "counts per group that are multiples of 8); there is no silent fallback" % prec)
         self.p = p
+        self.channels_last = bool(p.channels_last)
         self.deformable = deformable
         self.out_size = _lib.output_size(p)
         self.offset_channels = (x.size(1) // cpg) * int(torch.Size(weight.shape[2:]).numel()) * ndim
@@ -93,6 +101,22 @@ class Op:
         self.weight_shape = tuple(weight.shape)
 
     # -- helpers ---------------------------------------------------------------------------------
+    def _act(self, t: Optional[torch.Tensor], name: str, ref: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """An activation-like tensor (input, output gradient) in the storage order the problem was built for."""
+        t = _prep(t, name, ref) if not self.channels_last else t
+        if t is None or not self.channels_last:
+            return t
+        if not t.is_cuda:
+            raise DcnError("%s must be a CUDA tensor (there is no CPU implementation)" % name)
+        if ref is not None and (t.device != ref.device or t.dtype != ref.dtype):
+            raise DcnError("%s does not match the input's device / dtype" % name)
+        return t.contiguous(memory_format=self.memory_format)
+
+    def _new_act(self, shape, like: torch.Tensor, zero: bool = False) -> torch.Tensor:
+        mf = self.memory_format if self.channels_last else torch.contiguous_format
+        t = torch.empty(tuple(shape), dtype=like.dtype, device=like.device, memory_format=mf)
+        return t.zero_() if zero else t
+
     def _ws(self, which: int):
         nbytes = _lib.lib().dcn_workspace_bytes(ctypes.byref(self.p), which)
         if nbytes == 0:
@@ -110,13 +134,13 @@ class Op:
                  x_channels_last: Optional[torch.Tensor] = None):
         """All gradients through the fused entry point (outputs overwritten; scratch shared between the data
         and weight kernels).  ``x_channels_last``: the forward workspace kept by :meth:`forward` (bf16 path)."""
-        x = _prep(x, "input")
+        x = self._act(x, "input")
         weight = _prep(weight, "weight", x)
-        dy = _prep(dy, "grad_output", x)
+        dy = self._act(dy, "grad_output", x)
         offset = _prep(offset, "offset", x) if self.deformable else None
         if not self.deformable:
             want_doffset = False
-        dx = torch.empty_like(x) if want_dx else None
+        dx = self._new_act(x.shape, x) if want_dx else None
         doff = torch.empty_like(offset) if want_doffset else None
         dw = torch.empty(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
         db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
@@ -129,7 +153,7 @@ class Op:
         return dx, doff, dw, db
 
     def forward(self, x, offset, weight, bias=None, keep_workspace: bool = False):
-        x = _prep(x, "input")
+        x = self._act(x, "input")
         weight = _prep(weight, "weight", x)
         bias = _prep(bias, "bias", x)
         if self.deformable:
@@ -137,7 +161,7 @@ class Op:
             self._check_offset(offset)
         else:
             offset = None
-        y = torch.empty((self.N, self.O) + tuple(self.out_size), dtype=x.dtype, device=x.device)
+        y = self._new_act((self.N, self.O) + tuple(self.out_size), x)
         ws, nb = self._ws(_lib.PASS_FORWARD)
         with torch.cuda.device(x.device):
             st = _lib.lib().dcn_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
@@ -151,17 +175,17 @@ class Op:
     def backward_data(self, x, offset, weight, dy, want_dx=True, want_doffset=True
                       ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
         weight = _prep(weight, "weight")
-        dy = _prep(dy, "grad_output", weight)
+        dy = self._act(dy, "grad_output", weight)
         dx = doff = None
         if self.deformable:
-            x = _prep(x, "input", weight)
+            x = self._act(x, "input", weight)
             offset = _prep(offset, "offset", weight)
             self._check_offset(offset)
         else:
             offset = None
             want_doffset = False
         if want_dx:
-            dx = torch.zeros((self.N, self.C) + tuple(self.p.in_)[3 - self.ndim:], dtype=dy.dtype, device=dy.device)
+            dx = self._new_act((self.N, self.C) + tuple(self.p.in_)[3 - self.ndim:], dy, zero=True)
         if want_doffset:
             doff = torch.empty((self.N, self.offset_channels) + tuple(self.out_size), dtype=dy.dtype, device=dy.device)
         if dx is None and doff is None:
@@ -176,8 +200,8 @@ class Op:
 
     def backward_weight(self, x, offset, dy, want_dw=True, want_dbias=False
                         ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
-        x = _prep(x, "input")
-        dy = _prep(dy, "grad_output", x)
+        x = self._act(x, "input")
+        dy = self._act(dy, "grad_output", x)
         offset = _prep(offset, "offset", x) if self.deformable else None
         dw = torch.zeros(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
         db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None

@@ -73,6 +73,11 @@ typedef struct dcn_problem {
     int32_t G;                /* convolution groups */
     int32_t cpg;              /* channels per deformable group (the reference's channel_per_group) */
     int32_t in[3], k[3], stride[3], pad[3], dil[3];
+    int32_t channels_last;    /* 0: x, y and their gradients are [N, channels, spatial] as in the reference.
+                                 1: they are [N, spatial, channels] (torch channels_last / channels_last_3d
+                                 storage), so no layout pass runs around the kernels; offsets and their
+                                 gradient stay [N, dg*kv*D, out spatial], weights [O, C/G, k].  DCN_PREC_BF16
+                                 only.  The reference has no such layout (its tensors are always NCHW). */
 } dcn_problem;
 
 int dcn_version(void);

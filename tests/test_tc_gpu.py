@@ -72,3 +72,51 @@ def test_separate_bf16_passes_match_fused_backward(name):
     _check_status()
     for a, r in ((dx_f, dx_s), (doff_f, doff_s), (dw_f, dw_s), (db_f, db_s), (dx_n, dx_s), (dw_n, dw_s)):
         assert cases.rel_err(a.cpu().numpy(), r.cpu().numpy()) <= 1e-3
+
+
+@pytest.mark.parametrize("name", ["tc2_small", "tc2_dg_groups", "tc2_cpg16_tiles", "tc3_small", "tc3_groups", "tc3_o512"])
+def test_channels_last_io_matches_reference_layout(name):
+    """Channels-last activations (torch.channels_last / channels_last_3d storage) in and out of the bf16 path:
+    same arithmetic as the reference layout, no layout pass, results returned channels-last."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    case = {c.name: c for c in cases.TC_CASES}[name]
+    mf = torch.channels_last if case.ndim == 2 else torch.channels_last_3d
+    x, w, off, dy, b = [None if t is None else t.cuda() for t in cases.make_inputs(case)]
+    ref = dcn.Op(x, w, case.stride, case.pad, case.dil, case.cpg, case.G, precision="bf16")
+    assert not ref.channels_last
+    y_r = ref.forward(x, off, w, b)
+    dx_r, doff_r, dw_r, db_r = ref.backward(x, off, w, dy, True, True, True, True, None)
+    x_cl, dy_cl = x.contiguous(memory_format=mf), dy.contiguous(memory_format=mf)
+    op = dcn.Op(x_cl, w, case.stride, case.pad, case.dil, case.cpg, case.G, precision="bf16")
+    assert op.channels_last == (not x_cl.is_contiguous())
+    y_c, fws = op.forward(x_cl, off, w, b, keep_workspace=True)
+    dx_c, doff_c, dw_c, db_c = op.backward(x_cl, off, w, dy_cl, True, True, True, True, fws)
+    dx_s, doff_s = op.backward_data(x_cl, off, w, dy_cl)
+    dw_s, db_s = op.backward_weight(x_cl, off, dy_cl, True, True)
+    _check_status()
+    if op.channels_last:
+        assert y_c.is_contiguous(memory_format=mf) and dx_c.is_contiguous(memory_format=mf)
+    assert y_c.shape == y_r.shape and dx_c.shape == dx_r.shape
+    # the forward arithmetic is identical (same bf16 operands, same accumulation order inside a tile)
+    assert cases.rel_err(y_c.cpu().numpy(), y_r.cpu().numpy()) <= 1e-5
+    for a, r in ((dx_c, dx_r), (doff_c, doff_r), (dw_c, dw_r), (db_c, db_r), (dx_s, dx_r), (doff_s, doff_r),
+                 (dw_s, dw_r), (db_s, db_r)):
+        assert cases.rel_err(a.cpu().numpy(), r.cpu().numpy()) <= 1e-3
+
+
+def test_channels_last_needs_the_bf16_path():
+    import deform_conv3d_pytorch_op_b200 as dcn
+    from deform_conv3d_pytorch_op_b200 import _lib
+    import ctypes
+    p = _lib.make_problem(2, torch.float32, 2, 16, 16, (8, 8), (3, 3), 1, 1, 1, 1, 16, precision=_lib.PREC_EXACT,
+                          channels_last=True)
+    assert _lib.lib().dcn_validate(ctypes.byref(p)) == -3
+    # the tensor-level wrapper keeps the exact path on the reference layout and converts
+    x = torch.randn(2, 16, 8, 8).cuda().contiguous(memory_format=torch.channels_last)
+    w = torch.randn(16, 16, 3, 3).cuda()
+    off = torch.zeros(2, 18, 8, 8).cuda()
+    op = dcn.Op(x, w, 1, 1, 1, 16, 1, precision="exact")
+    assert not op.channels_last
+    y = op.forward(x, off, w, None)
+    ref = torch.nn.functional.conv2d(x.cpu().double(), w.cpu().double(), None, padding=1)      # zero offsets
+    assert cases.rel_err(y.cpu().numpy(), ref.numpy()) <= 1e-4
