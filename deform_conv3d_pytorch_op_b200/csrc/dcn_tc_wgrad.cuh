@@ -6,7 +6,8 @@
 //
 // GEMM view: M = output channels (128-row tiles, up to two per CTA), N = a block of up to 256 k' columns,
 // K = output positions, 64 per pipeline stage.  One CTA owns one (group, o-block, k'-block) and a slice of
-// the position range; partial sums are added to dW with fp32 atomics (dW is tiny and L2-resident).
+// the position range; partial sums are added with 16-byte fp32 reductions to the packed scratch dwpk[o][k']
+// (tiny and L2-resident), which unpack_dw folds into dW afterwards.
 //   A operand: dy, bf16, pre-packed by pack_dy into swizzled [128 o][64 P] tiles  -> K-major, bulk-copied
 //   B operand: sampled patch, [64 P rows][64 k' per 128-byte row] sub-tiles        -> MN-major, produced here
 #pragma once
