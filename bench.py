@@ -258,6 +258,55 @@ def run_model(args):
         dist.destroy_process_group()
 
 
+def run_probe(args):
+    """Rates of the access patterns that bound the tensor-core kernels, measured with the kernels' own lane layout
+    (8 lanes x 16 bytes = one 128-byte line, four pseudo-random lines per warp instruction): `scatter` =
+    red.global.add.v4.f32 into an fp32 buffer (the input-gradient epilogue), `gather` = 16-byte read-only loads
+    (the corner fetches).  Buffer sizes: config 2's dX (103 MB) / bf16 input copy (51 MB), and 16 MB for the
+    L2-resident case."""
+    import ctypes
+    from deform_conv3d_pytorch_op_b200 import _lib, build as _build
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _build.build()
+    lib = ctypes.CDLL(_build.PROBE_LIB)
+    lib.dcn_probe_scatter.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    lib.dcn_probe_gather.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                     ctypes.c_void_p]
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    sink = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = _lib.current_stream(dev)
+    out = {}
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    for name, nbytes in (("103MB", 32 * 256 * 56 * 56 * 4), ("51MB", 32 * 256 * 56 * 56 * 2), ("16MB", 16 << 20)):
+        buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=dev)
+        for kind in ("scatter", "gather"):
+            best = 0.0
+            for blocks_per_sm in (1, 2, 4):
+                blocks, reps = sms * blocks_per_sm, 512
+                def launch():
+                    if kind == "scatter":
+                        r = lib.dcn_probe_scatter(buf.data_ptr(), nbytes, blocks, reps, st)
+                    else:
+                        r = lib.dcn_probe_gather(buf.data_ptr(), nbytes, blocks, reps, sink.data_ptr(), st)
+                    assert r == 0, r
+                for _ in range(3):
+                    launch()
+                torch.cuda.synchronize()
+                a, b = ev(), ev()
+                a.record()
+                for _ in range(5):
+                    launch()
+                b.record()
+                torch.cuda.synchronize()
+                gbs = 5.0 * blocks * 512 * reps * 16 / (a.elapsed_time(b) * 1e-3) / 1e9
+                best = max(best, gbs)
+            out["%s_%s_gbs" % (kind, name)] = round(best, 1)
+    print(json.dumps({"probe": out, "sms": sms, "unit": "GB/s of 16-byte pieces, best of 1/2/4 CTAs of 512 threads per SM"}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,7 +324,12 @@ def main():
     ap.add_argument("--cpu-baseline-samples", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--probe", action="store_true",
+                    help="measure the two access patterns that bound the kernels (random 128-byte lines: 16-byte "
+                         "vector reductions, 16-byte gathers) and print their rates instead of the bench line")
     args = ap.parse_args()
+    if args.probe:
+        return run_probe(args)
 
     if args.config == 5:
         run_model(args)
