@@ -20,6 +20,9 @@ namespace tc {
 __device__ unsigned int g_tc_status;
 
 constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 2 GHz: far beyond any legitimate wait
+constexpr uint32_t kWaitParkNs = 20000;           // a waiting thread is parked up to this long per poll (woken at once
+                                                  // when the phase completes): fewer polling instructions next to the
+                                                  // working warps, measured -2..3 % on the 3-D backward kernels
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -67,7 +70,7 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_hint(bar, parity, kWaitParkNs)) {
         if (clock64() - t0 > kWaitCycles) {
             atomicOr(&g_tc_status, 1u);
             return false;

@@ -339,6 +339,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 continue;
             }
             // nothing to do yet: bounded wait for either event
+            __nanosleep(200);
             if (!waiting) {
                 waiting = true;
                 t0 = clock64();
@@ -376,6 +377,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         Ring rtab, rstg;            // table buffer and operand stage of the issue cursor
         bool failed = false;
         PROF_DECL
+        const uint32_t tab_s = smem_u32(tab);
+        const uint32_t pix_bytes = (uint32_t)g.C * 2u;
+        const __nv_bfloat16* xbase[RT];         // channels-last base of the sample of each of this thread's rows
         auto init_tile = [&]() {
             const int ks = (int)(ct % KS);
             const long long tt = ct / KS;
@@ -383,6 +387,13 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             cj = (int)(tt / PT / MB);
             ckc = ks * cpk;
             ckc_end = (ckc + cpk < KC) ? ckc + cpk : KC;
+#pragma unroll
+            for (int i = 0; i < RT; ++i) {
+                const long long P = cpt * kTileN + row0 + RS * i;
+                uint32_t n = 0;
+                if (P < g.P) n = g.d_ov.div((uint32_t)P);
+                xbase[i] = xcl + (size_t)n * g.iv * g.C;
+            }
         };
         auto next_stage = [&]() {
             rtab.next(n_tabs);
@@ -404,14 +415,17 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 g.d_Cg.divmod((uint32_t)(kp < g.kv * g.Cg ? kp : 0), tap, cl);
                 cc = cj * g.Cg + (int)cl;
             }
-            const Entry* trow = tab + ((size_t)tb * max_slots + csl) * 128;
+            const uint32_t trow_s = tab_s + ((tb * (uint32_t)max_slots + (uint32_t)csl) * 128u) * (uint32_t)sizeof(Entry);
 #pragma unroll
-            for (int r = 0; r < RPP; ++r) {
-                const int row = row0 + RS * (ch * RPP + r);
-                const long long P = cpt * kTileN + row;
-                uint32_t n = 0;
-                if (P < g.P) n = g.d_ov.div((uint32_t)P);
-                gather_issue_w<D, DEFORM>(trow + row, xcl + (size_t)n * g.iv * g.C + cc, g.C, p.q[r], p.w[r]);
+            for (int hh = 0; hh < PPS; ++hh) {
+                if (hh == ch) {
+#pragma unroll
+                    for (int r = 0; r < RPP; ++r) {
+                        const int i = hh * RPP + r;
+                        gather_issue_s<D, DEFORM>(trow_s + (uint32_t)(row0 + RS * i) * (uint32_t)sizeof(Entry),
+                                                  xbase[i] + cc, pix_bytes, p.q[r], p.w[r]);
+                    }
+                }
             }
             p.s = rstg.i;
             p.ph = rstg.ph;

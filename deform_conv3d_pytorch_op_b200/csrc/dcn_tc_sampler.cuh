@@ -228,6 +228,52 @@ __device__ __forceinline__ void gather_issue_w(const TabEntry<D, DEFORM>* ep, co
     }
 }
 
+// 16-byte shared-memory load from a 32-bit shared address (the compiler cannot always prove that a generic
+// pointer into the dynamic shared array is a shared address and then emits slower generic loads).
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
+    return v;
+}
+// base + a * b with a 32 x 32 -> 64-bit multiply-add: one instruction, where (size_t)a * b through C++ integer
+// promotion cost the producers a full 64-bit multiply per corner address.
+__device__ __forceinline__ const void* ptr_mad_u32(const void* base, uint32_t a, uint32_t b) {
+    uint64_t r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"(reinterpret_cast<uint64_t>(base)));
+    return reinterpret_cast<const void*>(r);
+}
+
+// Lean form of gather_issue_w: the entry at shared address `entry_s`, the 8 channels at `xrow` (sample base +
+// channel), `pix_bytes` = bytes between consecutive input positions of the channels-last copy.  Loads of an
+// invalid entry are predicated off (no divergent branch); its weights are zero.
+template <int D, bool DEFORM>
+__device__ __forceinline__ void gather_issue_s(uint32_t entry_s, const __nv_bfloat16* __restrict__ xrow,
+                                               uint32_t pix_bytes, uint4 (&q)[DEFORM ? (1 << D) : 1],
+                                               float (&w)[DEFORM ? (1 << D) : 1]) {
+    constexpr int NQ = DEFORM ? (1 << D) : 1;
+    constexpr int NI = DEFORM ? (1 << D) : 4;
+    uint32_t idx[NI];
+#pragma unroll
+    for (int i = 0; i < NI / 4; ++i) {
+        const uint4 t = lds128(entry_s + 16 * i);
+        idx[4 * i] = t.x; idx[4 * i + 1] = t.y; idx[4 * i + 2] = t.z; idx[4 * i + 3] = t.w;
+    }
+    if constexpr (DEFORM) {
+#pragma unroll
+        for (int i = 0; i < NQ / 4; ++i) {
+            const uint4 t = lds128(entry_s + 4 * NI + 16 * i);
+            w[4 * i] = __uint_as_float(t.x); w[4 * i + 1] = __uint_as_float(t.y);
+            w[4 * i + 2] = __uint_as_float(t.z); w[4 * i + 3] = __uint_as_float(t.w);
+        }
+    } else {
+        w[0] = 1.f;
+    }
+    const bool valid = (int)idx[0] >= 0;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i)
+        q[i] = valid ? __ldg(static_cast<const uint4*>(ptr_mad_u32(xrow, idx[i], pix_bytes))) : make_uint4(0, 0, 0, 0);
+}
+
 template <int D, bool DEFORM>
 __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 << D) : 1],
                                                  const float (&w)[DEFORM ? (1 << D) : 1]) {

@@ -233,6 +233,8 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             uint32_t s, ph;
             int h;
         };
+        const uint32_t tab_s = smem_u32(tab);
+        const uint32_t pix_bytes = (uint32_t)g.C * 2u;
         int cit = 0, ch = 0;
         Ring rtab, rstg;
         bool failed = false;
@@ -242,15 +244,16 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             if (ch == 0) {
                 if (!mbar_wait(&ctl->tab_full[tb], rtab.ph)) { failed = true; return false; }
             }
-            const Entry* trow = tab + ((size_t)tb * max_slots + sl) * 64;
+            const uint32_t trow_s = tab_s + ((tb * (uint32_t)max_slots + (uint32_t)sl) * 64u) * (uint32_t)sizeof(Entry);
 #pragma unroll
             for (int r = 0; r < RPP; ++r) {
                 const int row = row0 + RS * (ch * RPP + r);
                 const long long P = (c_begin + cit) * 64 + row;
-                uint32_t n = 0, opos = 0;
-                if (P < g.P) g.d_ov.divmod((uint32_t)P, n, opos);
+                uint32_t n = 0;
+                if (P < g.P) n = g.d_ov.div((uint32_t)P);
                 if (col_ok) {
-                    gather_issue_w<D, DEFORM>(trow + row, xcl + (size_t)n * g.iv * g.C + cch, g.C, p.q[r], p.w[r]);
+                    gather_issue_s<D, DEFORM>(trow_s + (uint32_t)row * (uint32_t)sizeof(Entry),
+                                              xcl + (size_t)n * g.iv * g.C + cch, pix_bytes, p.q[r], p.w[r]);
                 } else {
 #pragma unroll
                     for (int e = 0; e < NQ; ++e) { p.q[r][e] = make_uint4(0, 0, 0, 0); p.w[r][e] = 0.f; }

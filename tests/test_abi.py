@@ -31,6 +31,28 @@ def test_header_symbols_are_exported(L):
         assert sym in declared, sym
 
 
+def test_probe_library_is_separate_from_the_abi(L):
+    """bench.py --probe uses two access-pattern kernels; they live in their own library, not in libdcn.so."""
+    import ctypes
+    from deform_conv3d_pytorch_op_b200 import build
+    build.build()
+    probe = ctypes.CDLL(build.PROBE_LIB)
+    for sym in ("dcn_probe_scatter", "dcn_probe_gather"):
+        assert hasattr(probe, sym), sym
+        assert not hasattr(L, sym), sym
+
+
+def test_channels_last_is_a_bf16_option(L):
+    assert L.dcn_validate(ctypes.byref(_p(channels_last=True))) == -3            # exact precision: NCHW only
+    ok = _p(C=16, O=16, G=1, cpg=16, precision=_lib.PREC_BF16, channels_last=True)
+    assert L.dcn_validate(ctypes.byref(ok)) == 0
+    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 6        # no dx transpose pass
+    ok.channels_last = 0
+    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 7
+    ok.channels_last = 2
+    assert L.dcn_validate(ctypes.byref(ok)) == -3
+
+
 def _p(**kw):
     base = dict(ndim=2, dtype=torch.float32, N=2, C=4, O=6, in_size=(7, 7), kernel=(3, 3), stride=(1, 1), pad=(1, 1),
                 dil=(1, 1), G=2, cpg=2)
