@@ -40,7 +40,7 @@ int validate(const dcn_problem* p) {
         iv *= p->in[d]; ov *= o; kv *= p->k[d];
     }
     // index ranges the kernels assume (32-bit flattened positions and per-sample plane offsets)
-    if ((long long)p->N * ov >= (1ll << 31)) return DCN_ERR_LIMIT;
+    if ((long long)p->N * ov >= (1ll << 31) || (long long)p->N * iv >= (1ll << 31)) return DCN_ERR_LIMIT;
     if ((long long)p->C * iv >= (1ll << 31) || (long long)(p->C / p->G) * kv >= (1ll << 31)) return DCN_ERR_LIMIT;
     if (p->deformable && (long long)(p->C / p->cpg) * kv * p->ndim * ov >= (1ll << 31)) return DCN_ERR_LIMIT;
     return DCN_OK;

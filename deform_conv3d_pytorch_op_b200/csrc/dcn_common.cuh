@@ -122,7 +122,14 @@ __device__ __forceinline__ void locate_with(const Geom& g, const T (&offv)[D], i
 template <typename T, int D>
 __device__ __forceinline__ const T* offset_ptr(const Geom& g, const T* __restrict__ off_n, int grp, int tap,
                                                const OutPos& op) {
-    return off_n + ((size_t)(grp * g.kv + tap) * D) * g.ov + op.opos;
+    // (grp * kv + tap) * D * ov + opos stays below 2^31 inside one sample (checked on the host)
+    return off_n + (uint32_t)((grp * g.kv + tap) * D) * (uint32_t)g.ov + (uint32_t)op.opos;
+}
+
+// Offset block [dg*kv*D, ov] of sample n: one unsigned 32 x 32 -> 64-bit product instead of a chain of 64-bit ones.
+template <typename T, int D>
+__device__ __forceinline__ const T* offset_block(const Geom& g, const T* __restrict__ off, int n) {
+    return off + (uint64_t)(uint32_t)n * (uint64_t)(uint32_t)(g.dg * g.kv * D * g.ov);
 }
 
 // Locate one sampling point.  off_n points at the sample's offset block [dg*kv*D, ov].

@@ -111,14 +111,15 @@ template <int D, bool DEFORM>
 __device__ __forceinline__ uint4 sample_chunk(const Geom& g, const __nv_bfloat16* __restrict__ xcl,
                                               const float* __restrict__ off, const OutPos& op, int tap, int c,
                                               int grp) {
-    const __nv_bfloat16* xn = xcl + (size_t)op.n * g.iv * g.C + c;
+    const uint32_t pix_bytes = (uint32_t)g.C * 2u;
+    const void* xn = ptr_mad_u32(xcl + c, (uint32_t)op.n * (uint32_t)g.iv, pix_bytes);
     if (!DEFORM) {
         int idx;
         if (!locate_plain<D>(g, tap, op, idx)) return make_uint4(0, 0, 0, 0);
-        return __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx * g.C));
+        return __ldg(static_cast<const uint4*>(ptr_mad_u32(xn, (uint32_t)idx, pix_bytes)));
     }
     Pt<float, D> s;
-    locate<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op, s);
+    locate<float, D>(g, offset_block<float, D>(g, off, op.n), grp, tap, op, s);
     if (!s.valid) return make_uint4(0, 0, 0, 0);
     int idx[1 << D];
     float cw[1 << D];
@@ -126,7 +127,7 @@ __device__ __forceinline__ uint4 sample_chunk(const Geom& g, const __nv_bfloat16
     corner_weights<float, D>(s, cw);
     uint4 q[1 << D];
 #pragma unroll
-    for (int e = 0; e < (1 << D); ++e) q[e] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx[e] * g.C));
+    for (int e = 0; e < (1 << D); ++e) q[e] = __ldg(static_cast<const uint4*>(ptr_mad_u32(xn, (uint32_t)idx[e], pix_bytes)));
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;

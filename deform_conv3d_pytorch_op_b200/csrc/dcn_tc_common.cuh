@@ -194,6 +194,21 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// 16-byte shared-memory load from a 32-bit shared address (the compiler cannot always prove that a generic
+// pointer into the dynamic shared array is a shared address and then emits slower generic loads).
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
+    return v;
+}
+// base + a * b with a 32 x 32 -> 64-bit multiply-add: one instruction, where (size_t)a * b through C++ integer
+// promotion cost the producers a full 64-bit multiply per corner address.
+__device__ __forceinline__ const void* ptr_mad_u32(const void* base, uint32_t a, uint32_t b) {
+    uint64_t r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"(reinterpret_cast<uint64_t>(base)));
+    return reinterpret_cast<const void*>(r);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);

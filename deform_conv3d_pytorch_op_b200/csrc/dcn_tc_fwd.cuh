@@ -115,12 +115,15 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                     tc_fence_after();
                     const uint32_t a_base = smem_u32(smem + s * kFwdStageBytes);
                     const uint32_t b_base = a_base + 2 * kTileBytes;
+                    // one descriptor per operand and stage; the K step and the second M tile only move the
+                    // start-address field (units of 16 bytes), which cannot carry out of its 14 bits
+                    const uint64_t ad0 = make_desc(a_base, 16, 1024);
+                    const uint64_t bd0 = make_desc(b_base, 16, 1024);
                     for (int mt = 0; mt < mtb; ++mt) {
 #pragma unroll
                         for (int k = 0; k < kTileK / 16; ++k) {
-                            const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
-                            const uint64_t bd = make_desc(b_base + k * 32, 16, 1024);
-                            umma_bf16(tmem_base + b * 256 + mt * 128, ad, bd, kIdesc, (kc > kc0 || k > 0) ? 1u : 0u);
+                            umma_bf16(tmem_base + b * 256 + mt * 128, ad0 + (uint64_t)((mt * kTileBytes + k * 32) >> 4),
+                                      bd0 + (uint64_t)((k * 32) >> 4), kIdesc, (kc > kc0 || k > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(&ctl->empty[s]);
@@ -195,13 +198,14 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 for (int sl = 0; sl < si.nslots; ++sl) {
                     const int key = slot_key(si, sl);
                     if (key < 0) continue;
-                    const int grp = key / g.kv, tap = key - grp * g.kv;
+                    uint32_t grp, tap;
+                    g.d_kv.divmod((uint32_t)key, grp, tap);
 #pragma unroll
                     for (int i = 0; i < CR; ++i) {
                         const long long P = c.pt * kTileN + lane + 32 * i;
                         if (P >= g.P) continue;
                         const OutPos op = decompose_pos(g, P);
-                        const float* src = offset_ptr<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op);
+                        const float* src = offset_ptr<float, D>(g, offset_block<float, D>(g, off, op.n), (int)grp, (int)tap, op);
 #pragma unroll
                         for (int a = 0; a < D; ++a)
                             cp_async4(dst + (size_t)(sl * D + a) * 128 + lane + 32 * i, src + (size_t)a * g.ov);

@@ -74,7 +74,9 @@ __device__ __forceinline__ void fill_entry(const Geom& g, const float* __restric
         Pt<float, D> s;
         s.valid = false;
         if (pos_ok && key >= 0) {
-            const int grp = key / g.kv, tap = key - grp * g.kv;
+            uint32_t grp_, tap_;
+            g.d_kv.divmod((uint32_t)key, grp_, tap_);
+            const int grp = (int)grp_, tap = (int)tap_;
             locate<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op, s);
         }
         int idx[1 << D];
@@ -94,7 +96,7 @@ __device__ __forceinline__ void fill_entry(const Geom& g, const float* __restric
     } else {
         int pidx = -1;
         if (pos_ok && key >= 0) {
-            const int tap = key % g.kv;
+            const int tap = (int)((uint32_t)key - g.d_kv.div((uint32_t)key) * (uint32_t)g.kv);
             int t;
             if (locate_plain<D>(g, tap, op, t)) pidx = t;
         }
@@ -112,7 +114,9 @@ __device__ __forceinline__ void fill_entry_from(const Geom& g, const float (&off
         Pt<float, D> s;
         s.valid = false;
         if (pos_ok && key >= 0) {
-            const int grp = key / g.kv, tap = key - grp * g.kv;
+            uint32_t grp_, tap_;
+            g.d_kv.divmod((uint32_t)key, grp_, tap_);
+            const int tap = (int)tap_;
             locate_with<float, D>(g, offv, tap, op, s);
         }
         int idx[1 << D];
@@ -132,7 +136,7 @@ __device__ __forceinline__ void fill_entry_from(const Geom& g, const float (&off
     } else {
         int pidx = -1;
         if (pos_ok && key >= 0) {
-            const int tap = key % g.kv;
+            const int tap = (int)((uint32_t)key - g.d_kv.div((uint32_t)key) * (uint32_t)g.kv);
             int t;
             if (locate_plain<D>(g, tap, op, t)) pidx = t;
         }
@@ -152,6 +156,12 @@ __device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
 __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
 
@@ -228,21 +238,6 @@ __device__ __forceinline__ void gather_issue_w(const TabEntry<D, DEFORM>* ep, co
     }
 }
 
-// 16-byte shared-memory load from a 32-bit shared address (the compiler cannot always prove that a generic
-// pointer into the dynamic shared array is a shared address and then emits slower generic loads).
-__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr) : "memory");
-    return v;
-}
-// base + a * b with a 32 x 32 -> 64-bit multiply-add: one instruction, where (size_t)a * b through C++ integer
-// promotion cost the producers a full 64-bit multiply per corner address.
-__device__ __forceinline__ const void* ptr_mad_u32(const void* base, uint32_t a, uint32_t b) {
-    uint64_t r;
-    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(a), "r"(b), "l"(reinterpret_cast<uint64_t>(base)));
-    return reinterpret_cast<const void*>(r);
-}
-
 // Lean form of gather_issue_w: the entry at shared address `entry_s`, the 8 channels at `xrow` (sample base +
 // channel), `pix_bytes` = bytes between consecutive input positions of the channels-last copy.  Loads of an
 // invalid entry are predicated off (no divergent branch); its weights are zero.
@@ -279,14 +274,16 @@ __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 <<
                                                  const float (&w)[DEFORM ? (1 << D) : 1]) {
     if constexpr (!DEFORM) return q[0];
     else {
-        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
+        uint64_t acc[4];
 #pragma unroll
         for (int c = 0; c < (1 << D); ++c) {
             const uint64_t w2 = pack_f32x2(w[c], w[c]);
             const uint32_t wd[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                acc[i] = ffma2(w2, pack_f32x2(bf16_lo(wd[i]), bf16_hi(wd[i])), acc[i]);
+            for (int i = 0; i < 4; ++i) {
+                const uint64_t xv = pack_f32x2(bf16_lo(wd[i]), bf16_hi(wd[i]));
+                acc[i] = (c == 0) ? fmul2(w2, xv) : ffma2(w2, xv, acc[i]);       // 0 + w*x == w*x exactly
+            }
         }
         uint32_t out[4];
 #pragma unroll

@@ -100,12 +100,13 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 tc_fence_after();
                 const uint32_t a_base = smem_u32(smem + (size_t)s * stage_bytes);
                 const uint32_t b_base = a_base + a_tiles * kTileBytes;
+                const uint64_t ad0 = make_desc(a_base, 16, 1024);       // see dcn_tc_fwd.cuh: only the start address moves
+                const uint64_t bd0 = make_desc(b_base, 8192, 1024);
                 for (int mt = 0; mt < mtb; ++mt) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint64_t ad = make_desc(a_base + mt * kTileBytes + k * 32, 16, 1024);
-                        const uint64_t bd = make_desc(b_base + k * 2048, 8192, 1024);
-                        umma_bf16(tmem_base + mt * 256, ad, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_base + mt * 256, ad0 + (uint64_t)((mt * kTileBytes + k * 32) >> 4),
+                                  bd0 + (uint64_t)((k * 2048) >> 4), idesc, (it > 0 || k > 0) ? 1u : 0u);
                     }
                 }
                 umma_commit(&ctl->empty[s]);
@@ -146,8 +147,9 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     for (int sl = 0; sl < nslots; ++sl) {
                         const int key = ctl->key_of_slot[sl];
                         if (key < 0) continue;
-                        const int grp = key / g.kv, tap = key - grp * g.kv;
-                        const float* src = offset_ptr<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op);
+                        uint32_t grp, tap;
+                        g.d_kv.divmod((uint32_t)key, grp, tap);
+                        const float* src = offset_ptr<float, D>(g, offset_block<float, D>(g, off, op.n), (int)grp, (int)tap, op);
 #pragma unroll
                         for (int a = 0; a < D; ++a) cp_async4(dst + (size_t)(sl * D + a) * 64 + row, src + (size_t)a * g.ov);
                     }
