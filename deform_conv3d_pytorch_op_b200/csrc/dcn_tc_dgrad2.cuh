@@ -292,11 +292,14 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                             }
                         }
                     }
-                    const __nv_bfloat16* xb = xcl + (size_t)rd.n * g.iv * g.C + cbase;
+                    // unsigned 32 x 32 -> 64-bit products (one multiply-add each); plain C++ so that the pointers
+                    // stay provably global
+                    const __nv_bfloat16* xb = xcl + (uint64_t)((uint32_t)rd.n * (uint32_t)g.iv) * (uint32_t)g.C + cbase;
 #pragma unroll
                     for (int e = 0; e < NE; ++e)
-                        rd.xv[e] = (want_x && rd.valid) ? __ldg(reinterpret_cast<const uint2*>(xb + (size_t)rd.idx[e] * g.C))
-                                                        : make_uint2(0, 0);
+                        rd.xv[e] = (want_x && rd.valid)
+                                       ? __ldg(reinterpret_cast<const uint2*>(xb + (uint64_t)(uint32_t)rd.idx[e] * (uint32_t)g.C))
+                                       : make_uint2(0, 0);
                 };
                 auto consume = [&](int rr, const RowData& rd) {
                     const int row = rr * 4 + r4;
@@ -305,7 +308,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     for (int e = 0; e < NC; ++e) d[e] = 0.f;
                     float sabs = 0.f;
                     if (rd.valid) {
-                        float* db = dxcl + (size_t)rd.n * g.iv * g.C + cbase;
+                        float* db = dxcl + (uint64_t)((uint32_t)rd.n * (uint32_t)g.iv) * (uint32_t)g.C + cbase;
 #pragma unroll
                         for (int e = 0; e < NE; ++e) {
                             if (want_x) {
@@ -316,7 +319,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                             }
                             if (dxcl != nullptr) {
                                 const float wv = rd.cw[e];
-                                atomicAdd(reinterpret_cast<float4*>(db + (size_t)rd.idx[e] * g.C),
+                                atomicAdd(reinterpret_cast<float4*>(db + (uint64_t)(uint32_t)rd.idx[e] * (uint32_t)g.C),
                                           make_float4(wv * rd.c4.x, wv * rd.c4.y, wv * rd.c4.z, wv * rd.c4.w));
                             }
                         }

@@ -396,7 +396,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const long long P = cpt * kTileN + row0 + RS * i;
                 uint32_t n = 0;
                 if (P < g.P) n = g.d_ov.div((uint32_t)P);
-                xbase[i] = xcl + (size_t)n * g.iv * g.C;
+                xbase[i] = xcl + (uint64_t)(n * (uint32_t)g.iv) * (uint32_t)g.C;
             }
         };
         auto next_stage = [&]() {

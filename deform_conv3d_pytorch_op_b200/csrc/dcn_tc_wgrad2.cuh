@@ -255,7 +255,7 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                 if (P < g.P) n = g.d_ov.div((uint32_t)P);
                 if (col_ok) {
                     gather_issue_s<D, DEFORM>(trow_s + (uint32_t)row * (uint32_t)sizeof(Entry),
-                                              xcl + (size_t)n * g.iv * g.C + cch, pix_bytes, p.q[r], p.w[r]);
+                                              xcl + (uint64_t)(n * (uint32_t)g.iv) * (uint32_t)g.C + cch, pix_bytes, p.q[r], p.w[r]);
                 } else {
 #pragma unroll
                     for (int e = 0; e < NQ; ++e) { p.q[r][e] = make_uint4(0, 0, 0, 0); p.w[r][e] = 0.f; }
