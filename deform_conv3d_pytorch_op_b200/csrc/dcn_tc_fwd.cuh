@@ -47,14 +47,40 @@ struct FwdCtl {            // lives behind the stages, the tables and the offset
     int slot_of_chunk[kFwdMaxTabs][8];
 };
 
+// How the work items of the persistent CTAs map to (tile, K range).  Items [0, T0) split every tile KS0 ways
+// (KS0 = 1: whole tiles); items from T0 on split the tiles from tile1 on KS1 ways.  The second region is the
+// tail of a grid that does not divide evenly: the tiles left over after the last full wave are split along K so
+// that the last wave is a fraction of a tile long instead of a whole one.  Split tiles add into a zero-filled y.
+struct FwdSplit {
+    long long T0, tile1, n_items;
+    int KS0, cpk0, KS1, cpk1;
+};
+struct FwdItem {
+    long long tt;       // tile index ((j * MB + mb) * PT + pt)
+    int ks, kc0, kc1;   // split number and its K chunks [kc0, kc1)
+    bool atomic;        // partial sum of a split tile
+};
+__device__ __forceinline__ FwdItem fwd_item(const FwdSplit& sp, long long t, int KC) {
+    const bool tail = t >= sp.T0;
+    const long long r = tail ? t - sp.T0 : t;
+    const int KS = tail ? sp.KS1 : sp.KS0, cpk = tail ? sp.cpk1 : sp.cpk0;
+    FwdItem it;
+    it.ks = (int)(r % KS);
+    it.tt = (tail ? sp.tile1 : 0) + r / KS;
+    it.kc0 = it.ks * cpk;
+    it.kc1 = (it.kc0 + cpk < KC) ? it.kc0 + cpk : KC;
+    it.atomic = KS > 1;
+    return it;
+}
+
 template <int D, bool DEFORM, int GW>
 __global__ void __launch_bounds__(fwd_threads(GW), 1)
 tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float* __restrict__ off,
                   const uint8_t* __restrict__ wpk, const float* __restrict__ bias, float* __restrict__ y,
                   const int KC, const int MT, const int MB, const long long PT, const int n_stages,
-                  const int max_slots, const int n_tabs, const int KS, const int cpk) {
-    // Work item t = ((j * MB + mb) * PT + pt) * KS + ks: split ks owns K chunks [ks*cpk, min(KC, (ks+1)*cpk)).
-    // With KS > 1 (few position tiles, long K) the partial sums are added to a zero-filled y with atomics.
+                  const int max_slots, const int n_tabs, const FwdSplit sp) {
+    // Work items: see FwdSplit.  With few position tiles and a long K every tile is split (small batches, late
+    // layers of a network); otherwise only the tiles of the last, partial wave are.
     using Entry = TabEntry<D, DEFORM>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -89,7 +115,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    const long long n_tiles = (long long)g.G * MB * PT * KS;
+    const long long n_tiles = sp.n_items;
     constexpr uint32_t kIdesc = make_idesc(128, kTileN, 0, 0);
 
     if (warp == 0) {
@@ -100,11 +126,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             Ring rs;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tl) {
-                const int ks = (int)(t % KS);
-                const long long tt = t / KS;
+                const FwdItem wi = fwd_item(sp, t, KC);
+                const long long tt = wi.tt;
                 const int mb = (int)((tt / PT) % MB);
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
-                const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
+                const int kc0 = wi.kc0, kc1 = wi.kc1;
                 const uint32_t b = tl & 1;
                 { PROF_T0 ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1); PROF_ADD(0) }
                 tc_fence_after();
@@ -138,12 +164,12 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             Ring rs;
             bool ok = true;
             for (long long t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-                const int ks = (int)(t % KS);
-                const long long tt = t / KS;
+                const FwdItem wi = fwd_item(sp, t, KC);
+                const long long tt = wi.tt;
                 const int mb = (int)((tt / PT) % MB);
                 const int j = (int)(tt / PT / MB);
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
-                const int kc0 = ks * cpk, kc1 = (kc0 + cpk < KC) ? kc0 + cpk : KC;
+                const int kc0 = wi.kc0, kc1 = wi.kc1;
                 for (int kc = kc0; kc < kc1 && ok; ++kc, rs.next(n_stages)) {
                     const uint32_t s = rs.i;
                     ok = mbar_wait(&ctl->empty[s], rs.ph ^ 1u);
@@ -167,12 +193,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             uint32_t tl;            // how many tiles of this CTA came before t
         };
         auto init_tile = [&](Cur& c) {
-            const int ks = (int)(c.t % KS);
-            const long long tt = c.t / KS;
-            c.pt = tt % PT;
-            c.j = (int)(tt / PT / MB);
-            c.kc = ks * cpk;
-            c.kc_end = (c.kc + cpk < KC) ? c.kc + cpk : KC;
+            const FwdItem wi = fwd_item(sp, c.t, KC);
+            c.pt = wi.tt % PT;
+            c.j = (int)(wi.tt / PT / MB);
+            c.kc = wi.kc0;
+            c.kc_end = wi.kc1;
         };
         auto skip = [&](Cur& c, int n) {            // n stages further
             for (int i = 0; i < n && c.t < n_tiles; ++i) {
@@ -244,8 +269,10 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 waiting = false;
                 tc_fence_after();
                 const uint32_t b = etl & 1;
-                const int ks = (int)(et % KS);
-                const long long tt = et / KS;
+                const FwdItem wi = fwd_item(sp, et, KC);
+                const int ks = wi.ks;
+                const bool plain = !wi.atomic;
+                const long long tt = wi.tt;
                 const long long pt = tt % PT;
                 const int mb = (int)((tt / PT) % MB);
                 const int j = (int)(tt / PT / MB);
@@ -268,7 +295,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                             for (int i = 0; i < 16; ++i) {
                                 if (P0 + i < g.P) {
                                     float* d1 = y + (size_t)(P0 + i) * g.O + o;
-                                    if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
+                                    if (plain) *d1 = __uint_as_float(v[i]) + bv;
                                     else atomicAdd(d1, __uint_as_float(v[i]) + bv);
                                 }
                             }
@@ -283,7 +310,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                             for (int i = 0; i < 4; ++i) {
                                 const float4 val = make_float4(__uint_as_float(v[4 * i]) + bv, __uint_as_float(v[4 * i + 1]) + bv,
                                                                __uint_as_float(v[4 * i + 2]) + bv, __uint_as_float(v[4 * i + 3]) + bv);
-                                if (KS == 1) *reinterpret_cast<float4*>(dst + 4 * i) = val;
+                                if (plain) *reinterpret_cast<float4*>(dst + 4 * i) = val;
                                 else atomicAdd(reinterpret_cast<float4*>(dst + 4 * i), val);
                             }
                         } else {
@@ -294,7 +321,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                                     uint32_t n, opos;
                                     g.d_ov.divmod((uint32_t)P, n, opos);
                                     float* d1 = y + ((size_t)n * g.O + o) * g.ov + opos;
-                                    if (KS == 1) *d1 = __uint_as_float(v[i]) + bv;
+                                    if (plain) *d1 = __uint_as_float(v[i]) + bv;
                                     else atomicAdd(d1, __uint_as_float(v[i]) + bv);
                                 }
                             }
@@ -385,12 +412,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         const uint32_t pix_bytes = (uint32_t)g.C * 2u;
         const __nv_bfloat16* xbase[RT];         // channels-last base of the sample of each of this thread's rows
         auto init_tile = [&]() {
-            const int ks = (int)(ct % KS);
-            const long long tt = ct / KS;
-            cpt = tt % PT;
-            cj = (int)(tt / PT / MB);
-            ckc = ks * cpk;
-            ckc_end = (ckc + cpk < KC) ? ckc + cpk : KC;
+            const FwdItem wi = fwd_item(sp, ct, KC);
+            cpt = wi.tt % PT;
+            cj = (int)(wi.tt / PT / MB);
+            ckc = wi.kc0;
+            ckc_end = wi.kc1;
 #pragma unroll
             for (int i = 0; i < RT; ++i) {
                 const long long P = cpt * kTileN + row0 + RS * i;
@@ -535,18 +561,57 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -5;
     // split the K range when there are fewer tiles than SMs (small batches / late layers of a network)
     const long long base_tiles = (long long)g.G * d.MB * d.PT;
-    int KS = 1;
-    if (base_tiles * 2 <= sm_count()) {
-        KS = (int)(sm_count() / base_tiles);
-        if (KS > d.KC / 8) KS = d.KC / 8;          // at least 8 chunks per split
-        if (KS < 1) KS = 1;
+    const int S = sm_count();
+    FwdSplit sp;
+    sp.KS0 = 1;
+    if (base_tiles * 2 <= S) {
+        sp.KS0 = (int)(S / base_tiles);
+        if (sp.KS0 > d.KC / 8) sp.KS0 = d.KC / 8;          // at least 8 chunks per split
+        if (sp.KS0 < 1) sp.KS0 = 1;
     }
-    const int cpk = (d.KC + KS - 1) / KS;
-    KS = (d.KC + cpk - 1) / cpk;
-    if (KS > 1 && cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
-    const long long tiles = base_tiles * KS;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    kern<<<grid, fwd_threads(GW), smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs,
-                                          KS, cpk);
+    sp.cpk0 = (d.KC + sp.KS0 - 1) / sp.KS0;
+    sp.KS0 = (d.KC + sp.cpk0 - 1) / sp.cpk0;
+    sp.T0 = base_tiles * sp.KS0;
+    sp.tile1 = base_tiles;
+    sp.KS1 = 1;
+    sp.cpk1 = d.KC;
+    sp.n_items = sp.T0;
+    if (sp.KS0 > 1) {
+        if (cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
+    } else if (g.G * d.MB == 1 && base_tiles > S && base_tiles % S != 0) {
+        // Tail of an uneven grid: the R tiles left after the last full wave are split along K into as many pieces
+        // as there are SMs to take them.  With one (group, channel block) the tile index is the position tile, so
+        // the tail is the position range [P0, P) and only that part of y is zero-filled.
+        const long long R = base_tiles % S;
+        int ks1 = (int)(S / R);
+        if (ks1 > d.KC / 8) ks1 = d.KC / 8;
+        if (ks1 >= 2) {
+            sp.cpk1 = (d.KC + ks1 - 1) / ks1;
+            sp.KS1 = (d.KC + sp.cpk1 - 1) / sp.cpk1;
+            sp.T0 = base_tiles - R;
+            sp.tile1 = sp.T0;
+            sp.n_items = sp.T0 + R * sp.KS1;
+            const long long P0 = sp.T0 * kTileN;
+            if (g.cl) {
+                if (cudaMemsetAsync(y + (size_t)P0 * g.O, 0, (size_t)(g.P - P0) * g.O * sizeof(float), st) != cudaSuccess)
+                    return -5;
+            } else {
+                long long n0 = P0 / g.ov;
+                const long long o0 = P0 % g.ov;
+                if (o0 != 0) {      // the sample the tail starts in: the positions [o0, ov) of every channel
+                    if (cudaMemset2DAsync(y + (size_t)n0 * g.O * g.ov + o0, (size_t)g.ov * sizeof(float), 0,
+                                          (size_t)(g.ov - o0) * sizeof(float), (size_t)g.O, st) != cudaSuccess)
+                        return -5;
+                    ++n0;
+                }
+                if (n0 < g.N &&
+                    cudaMemsetAsync(y + (size_t)n0 * g.O * g.ov, 0, (size_t)(g.N - n0) * g.O * g.ov * sizeof(float), st) !=
+                        cudaSuccess)
+                    return -5;
+            }
+        }
+    }
+    const int grid = (int)(sp.n_items < S ? sp.n_items : S);
+    kern<<<grid, fwd_threads(GW), smem, st>>>(g, xcl, off, wpk, bias, y, d.KC, d.MT, d.MB, d.PT, stages, max_slots, n_tabs, sp);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -100,6 +100,9 @@ TC_CASES = [
     # four (deformable group, tap) keys per 64-channel chunk and more position tiles than SMs: the large corner
     # tables leave two operand stages, and CTAs with a second tile drain an accumulator between tables
     Case("tc2_cpg16_tiles", 2, 8, 64, 64, (50, 50), (3, 3), (1, 1), (1, 1), (1, 1), 1, 16, offset_std=2.5),
+    # 157 position tiles on 148 SMs with 18 K chunks: the nine tiles of the partial last wave are split along K
+    # and add into the zero-filled tail of y (which starts inside a sample)
+    Case("tc2_c128_tail", 2, 8, 128, 64, (50, 50), (3, 3), (1, 1), (1, 1), (1, 1), 1, 32, offset_std=2.0, bias=True),
 ]
 
 # --- BASELINE configurations 1-4 ------------------------------------------------------------------------

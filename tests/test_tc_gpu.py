@@ -74,7 +74,8 @@ def test_separate_bf16_passes_match_fused_backward(name):
         assert cases.rel_err(a.cpu().numpy(), r.cpu().numpy()) <= 1e-3
 
 
-@pytest.mark.parametrize("name", ["tc2_small", "tc2_dg_groups", "tc2_cpg16_tiles", "tc3_small", "tc3_groups", "tc3_o512"])
+@pytest.mark.parametrize("name", ["tc2_small", "tc2_dg_groups", "tc2_cpg16_tiles", "tc2_c128_tail", "tc3_small", "tc3_groups",
+                                  "tc3_o512"])
 def test_channels_last_io_matches_reference_layout(name):
     """Channels-last activations (torch.channels_last / channels_last_3d storage) in and out of the bf16 path:
     same arithmetic as the reference layout, no layout pass, results returned channels-last."""
