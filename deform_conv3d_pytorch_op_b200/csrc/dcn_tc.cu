@@ -52,22 +52,24 @@ TcDims tc_dims(const Geom& g) {
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 to_channels_last_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ xcl, int C, int iv) {
-    __shared__ float tile[32][33];
+    // tile of 64 channels x 32 positions: 128-byte reads along the positions, 128-byte writes of bf16 pairs along
+    // the channels (C is a multiple of 8, so a pair never straddles the end)
+    __shared__ float tile[64][33];
     const int n = blockIdx.z;
-    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 64;
     const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
     const float* xn = x + (size_t)n * C * iv;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
         const int c = c0 + ty + i * 8, p = p0 + tx;
-        tile[ty + i * 8][tx] = (c < C && p < iv) ? xn[(size_t)c * iv + p] : 0.f;
+        tile[ty + i * 8][tx] = (c < C && p < iv) ? __ldg(xn + (size_t)c * iv + p) : 0.f;
     }
     __syncthreads();
-    __nv_bfloat16* on = xcl + (size_t)n * iv * C;
+    uint32_t* on = reinterpret_cast<uint32_t*>(xcl + (size_t)n * iv * C);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int p = p0 + ty + i * 8, c = c0 + tx;
-        if (p < iv && c < C) on[(size_t)p * C + c] = __float2bfloat16_rn(tile[tx][ty + i * 8]);
+        const int p = p0 + ty + i * 8, c = c0 + 2 * tx;
+        if (p < iv && c < C) on[((size_t)p * C + c) >> 1] = pack_bf16x2(tile[2 * tx][ty + i * 8], tile[2 * tx + 1][ty + i * 8]);
     }
 }
 
@@ -188,7 +190,7 @@ int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cuda
         cast_bf16<<<blocks, 256, 0, st>>>(x, xcl, n8);
         return cudaGetLastError() == cudaSuccess ? 0 : -5;
     }
-    dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+    dim3 grid((unsigned)((g.iv + 31) / 32), (unsigned)((g.C + 63) / 64), (unsigned)g.N);
     to_channels_last_bf16<<<grid, 256, 0, st>>>(x, xcl, g.C, g.iv);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
