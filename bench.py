@@ -546,6 +546,17 @@ def main():
         t_gs = 3.0 * wl.bytes_gather_scatter() / (peaks["hbm_gbs"] * 1e9)
         roof.update({"gather_scatter": {"bytes_per_pass": wl.bytes_gather_scatter(), "passes": 3,
                                         "t_roof_ms": t_gs * 1e3, "frac": t_gs / (ms_per_step * 1e-3)}})
+        # third reading, for the input-gradient pass only: its fp32 vector reductions against the rate the same
+        # access pattern reaches alone (bench.py --probe, committed under profiles/)
+        ppath = os.path.join(ROOT, "profiles", "access_pattern_probes.json")
+        if os.path.exists(ppath) and prec == "bf16":
+            with open(ppath) as f:
+                pj = json.load(f)
+            ach = wl.bytes_gather_scatter() / (pass_ms["backward_data"] * 1e-3) / 1e9
+            roof["scatter_path"] = {"pass": "backward_data", "bytes": wl.bytes_gather_scatter(), "achieved": ach,
+                                    "peak": pj["scatter_red_v4_gbs"], "unit": "GB/s",
+                                    "frac": ach / pj["scatter_red_v4_gbs"],
+                                    "peak_source": "profiles/access_pattern_probes.json (bench.py --probe)"}
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic_cfg%d.json" % args.config)
         if os.path.exists(tpath):            # DRAM bytes of the dominant kernel from the committed ncu capture, scaled
