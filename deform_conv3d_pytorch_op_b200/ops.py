@@ -74,7 +74,7 @@ class Op:
                                           channels_last and pr == _lib.PREC_BF16)
         if prec == "auto":
             # bf16 tensor-core path where the shape allows it and the problem is big enough to pay for its
-            # layout pre-passes (eleven launches per step against three of the exact path)
+            # layout pre-passes (ten launches per step against three of the exact path)
             kvol = int(torch.Size(weight.shape[2:]).numel())
             out_guess = 1
             for i, k_, s_, p_ in zip(x.shape[2:], weight.shape[2:], _lib._triple(stride, ndim, 1)[3 - ndim:],
