@@ -63,3 +63,29 @@ def test_static_scratch_forward_matches_workspace_forward(name):
         assert np.isfinite(a).all() and np.isfinite(r).all()
         assert cases.rel_err(a, r) <= TOL_BF16, cases.rel_err(a, r)
         assert np.array_equal(a, r)                        # same kernels, same inputs: identical bits
+
+
+@pytest.mark.gpu
+def test_static_scratch_forward_takes_channels_last_activations():
+    """Same entry point with dcn_problem.channels_last = 1: x and y are [N, spatial, channels]."""
+    from deform_conv3d_pytorch_op_b200 import _lib
+    L = _lib.lib()
+    case = {c.name: c for c in cases.TC_CASES}["tc2_small"]
+    dev = torch.device("cuda")
+    stream = _lib.current_stream(dev)
+    prob = _problem(case)
+    x, w, off, dy, b = [None if t is None else t.to(dev) for t in cases.make_inputs(case)]
+    out_shape = (case.N, case.O) + _lib.output_size(prob)
+    y_ref = torch.empty(out_shape, device=dev)
+    _lib.check(L.dcn_forward_static_scratch(ctypes.byref(prob), _lib.ptr(x), _lib.ptr(off), _lib.ptr(w), _lib.ptr(b),
+                                            _lib.ptr(y_ref), stream), "reference layout")
+    prob.channels_last = 1
+    x_cl = x.permute(0, 2, 3, 1).contiguous()                        # [N, H, W, C]
+    y_cl = torch.full((case.N,) + _lib.output_size(prob) + (case.O,), float("nan"), device=dev)
+    _lib.check(L.dcn_forward_static_scratch(ctypes.byref(prob), _lib.ptr(x_cl), _lib.ptr(off), _lib.ptr(w),
+                                            _lib.ptr(b), _lib.ptr(y_cl), stream), "channels last")
+    torch.cuda.synchronize()
+    _lib.check(L.dcn_check_status(stream), "device status")
+    a, r = y_cl.permute(0, 3, 1, 2).cpu().numpy(), y_ref.cpu().numpy()
+    assert np.isfinite(a).all()
+    assert cases.rel_err(a, r) <= 1e-5, cases.rel_err(a, r)
