@@ -37,8 +37,7 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
     const bool ok0 = P0 < g.P, ok1 = P0 + 1 < g.P;
     if (ok0) g.d_ov.divmod((uint32_t)P0, n0, op0);
     if (ok1) g.d_ov.divmod((uint32_t)(P0 + 1), n1, op1);
-#pragma unroll 8
-    for (int row = wrp; row < 128; row += 8) {      // 16 rows per warp; unrolled so that the loads are in flight together
+    for (int row = wrp; row < 128; row += 8) {      // (forcing this loop to unroll 8-fold measured 20 % slower)
         const int ol = mt * 128 + row;
         float a = 0.f, b = 0.f;
         if (ol < g.Og) {
