@@ -21,11 +21,8 @@ constexpr int kDg2Stages = 2;
 
 template <int D, bool DEFORM>
 struct alignas(16) DgEntry {
-    int idx[1 << D];
+    int idx[1 << D];  // corner positions in the whole channels-last tensor (sample * in volume + corner); idx[0] < 0: invalid
     float cw[1 << D];
-    int n;            // sample index
-    int valid;
-    int pad[2];
 };
 
 template <int D, bool DEFORM, int EW, int U>
@@ -224,9 +221,9 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     key[sl] = nkey[sl];
                     // phase A: locate the point of the new key and publish it; reset the key's accumulators
                     Entry e;
-                    e.n = op.n; e.valid = 0; e.pad[0] = e.pad[1] = 0;
 #pragma unroll
-                    for (int i = 0; i < NC; ++i) { e.idx[i] = 0; e.cw[i] = 0.f; }
+                    for (int i = 0; i < NC; ++i) { e.idx[i] = -1; e.cw[i] = 0.f; }
+                    const int nbase = op.n * g.iv;            // N * in volume < 2^31 (checked on the host)
                     pts[sl].valid = false;
                     if (p_ok && nkey[sl] >= 0) {
                         if (DEFORM) {
@@ -235,13 +232,13 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                             if (pts[sl].valid) {
                                 corner_indices<float, D>(g, pts[sl], e.idx);
                                 corner_weights<float, D>(pts[sl], e.cw);
-                                e.valid = 1;
+#pragma unroll
+                                for (int i = 0; i < NC; ++i) e.idx[i] += nbase;
                             }
                         } else {
                             int pidx;
                             if (locate_plain<D>(g, nkey[sl], op, pidx)) {
-                                e.valid = 1;
-                                e.idx[0] = pidx;
+                                e.idx[0] = nbase + pidx;
                                 e.cw[0] = 1.f;
                             }
                         }
@@ -269,15 +266,12 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     float cw[NE];
                     int idx[NE];
                     uint2 xv[NE];
-                    int n, valid;
+                    int valid;
                 };
                 auto fetch = [&](int rr, RowData& rd) {
                     const int row = rr * 4 + r4;
                     const Entry* ep = ent + my_slot * 32 + row;
-                    const int4 hdr = *reinterpret_cast<const int4*>(&ep->n);      // n, valid, pad, pad
                     rd.c4 = *reinterpret_cast<const float4*>(colS + row * 36 + cq * 4);
-                    rd.valid = lane_ok ? hdr.y : 0;
-                    rd.n = hdr.x;
 #pragma unroll
                     for (int i = 0; i < (NE + 3) / 4; ++i) {
                         const int4 ti = reinterpret_cast<const int4*>(ep->idx)[i];
@@ -294,7 +288,8 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     }
                     // unsigned 32 x 32 -> 64-bit products (one multiply-add each); plain C++ so that the pointers
                     // stay provably global
-                    const __nv_bfloat16* xb = xcl + (uint64_t)((uint32_t)rd.n * (uint32_t)g.iv) * (uint32_t)g.C + cbase;
+                    rd.valid = (lane_ok && rd.idx[0] >= 0) ? 1 : 0;
+                    const __nv_bfloat16* xb = xcl + cbase;
 #pragma unroll
                     for (int e = 0; e < NE; ++e)
                         rd.xv[e] = (want_x && rd.valid)
@@ -308,7 +303,7 @@ tc_dgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     for (int e = 0; e < NC; ++e) d[e] = 0.f;
                     float sabs = 0.f;
                     if (rd.valid) {
-                        float* db = dxcl + (uint64_t)((uint32_t)rd.n * (uint32_t)g.iv) * (uint32_t)g.C + cbase;
+                        float* db = dxcl + cbase;
 #pragma unroll
                         for (int e = 0; e < NE; ++e) {
                             if (want_x) {
