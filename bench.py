@@ -23,10 +23,31 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+
+def _host_threads() -> int:
+    """Host threads for the CPU legs (the reference arm and cpu_baseline): every core this process may run on.
+    torchrun exports OMP_NUM_THREADS=1 to its workers, which would silently turn a "16 cores" baseline into a
+    one-thread run; the count is therefore set explicitly, before numpy / torch load their OpenMP and BLAS
+    runtimes, on the one rank that runs a CPU leg (rank 0; with several ranks only the reference arm has one)."""
+    return len(os.sched_getaffinity(0))
+
+
+if int(os.environ.get("RANK", "0")) == 0 and ("reference" in sys.argv or int(os.environ.get("WORLD_SIZE", "1")) == 1):
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(_host_threads())
+
 import torch  # noqa: E402
 
 METRIC = "deform_conv_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
+
+# (config, pass) -> (dram__bytes_read.sum + dram__bytes_write.sum of the pass's main kernel in one ncu capture,
+# output positions of the captured launch).  Figures and commands: profiles/tc_*_cfg2_*.md.
+NCU_DRAM_BYTES = {
+    (2, "forward"): (117862400, 25088),
+    (2, "backward_data"): (67954688, 25088),
+    (2, "backward_weight"): (40454912, 25088),
+}
 
 
 def _peaks():
@@ -100,14 +121,75 @@ def cpu_port_run(wl, n_samples: int, repeats: int = 1):
     return best
 
 
+def _omp_threads() -> int:
+    """Threads the OpenMP runtime of the oracle library will actually use."""
+    import ctypes
+    for name in ("libgomp.so.1", "libomp.so", "libiomp5.so"):
+        try:
+            return int(ctypes.CDLL(name).omp_get_max_threads())
+        except OSError:
+            continue
+    return int(os.environ.get("OMP_NUM_THREADS", "1"))
+
+
+def our_config(wl, prec: str, world: int, flush: bool, working_set: float) -> dict:
+    """The `config` object of the JSON line; both arms print the same one for the same workload."""
+    return {"workload": wl.name, "per_gpu_batch": wl.N, "precision": prec, "io_dtype": "f32",
+            "l2": "flushed between steps" if flush else "working set %.0f MB > 126 MB L2" % (working_set / 1e6),
+            "parallelism": "batch-sharded x%d, dW all-reduce" % world if world > 1 else "single GPU"}
+
+
+def workload_l2(wl):
+    """(working set in bytes, whether the bench flushes L2 between steps)."""
+    x = wl.N * wl.C * wl.iv
+    off = wl.N * wl.offset_channels * wl.ov
+    dy = wl.N * wl.O * wl.ov
+    ws = (x + off + dy) * 4 * 2 + x * 4
+    return ws, ws < 512 * 1024 * 1024
+
+
+def reference_kernels_run(wl, dev):
+    """The reference's own device kernels (its lib/*_kernel.cu compiled unmodified for sm_100a into oracle/_ref)
+    driven by the reference's host loop (serial over the batch, one GEMM per group through torch.mm where the
+    reference calls cuBLAS SGEMM): forward + both backward passes of the whole batch on this GPU.  Part of the
+    baseline leg, outside every timed region of the operator.  None where oracle/_ref is not built or the
+    reference has no fp32 package for the shape (2-D with dilation or groups)."""
+    from oracle import ref_gpu, oracle as orc
+    if not ref_gpu.available():
+        return None
+    if wl.ndim == 2 and (tuple(wl.dil) != (1, 1) or wl.G != 1):
+        return None
+    from deform_conv3d_pytorch_op_b200 import workloads
+    variant = "deform3d" if wl.ndim == 3 else "deform2d"
+    p = orc.Problem(wl.ndim, wl.N, wl.C, wl.O, wl.in_size, wl.kernel, wl.stride, wl.pad, wl.dil, wl.G, wl.cpg)
+    x, w, off, dy = [t.to(dev) for t in workloads.make_inputs(wl)]
+    op = ref_gpu.RefOp(variant, p)
+
+    def once():
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        op.forward(x, off, w)
+        op.backward_data(x, off, w, dy)
+        op.backward_weight(x, off, dy)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t0
+    once()
+    dt = min(once(), once())
+    return {"value": wl.flops() / dt / 1e12, "unit": UNIT, "ms_per_step": dt * 1e3,
+            "what": "reference %s kernels (unmodified, sm_100a build) + torch.mm fp32 GEMMs, per-sample host loop "
+                    "with a device synchronisation around every kernel launch, whole batch" % variant}
+
+
 def run_reference(args, wl):
     """--impl reference: the reference algorithm on the host cores.  The reference ships CUDA kernels only
-    and no CPU path, so this is the oracle port (kind "port"), with all host threads (OpenMP + BLAS)."""
+    and no CPU path, so this is the oracle port (kind "port"), with all host threads (OpenMP + BLAS).  One step
+    is the whole per-GPU batch unless --ref-samples bounds it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = len(os.sched_getaffinity(0))
-    n = max(1, min(wl.N, args.ref_samples))
+    cores = _host_threads()
+    torch.set_num_threads(cores)
+    n = wl.N if args.ref_samples <= 0 else max(1, min(wl.N, args.ref_samples))
     from oracle import oracle as orc
     orc.build()
     for _ in range(args.warmup):
@@ -118,12 +200,16 @@ def run_reference(args, wl):
     dt = (time.perf_counter() - t0) / args.steps
     val = wl.flops(n) / dt / 1e12
     sample = "%d of %d samples per step, forward + backward (dX, dOffset, dW), fp32" % (n, wl.N)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    ws, flush = workload_l2(wl)
+    prec = "exact" if (args.precision == "exact" or (args.precision == "auto" and args.config == 1)) else "bf16"
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl.name, "samples_per_step": n},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": our_config(wl, prec, world, flush, ws),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "omp_threads": _omp_threads(), "kind": "port",
+                         "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -258,55 +344,6 @@ def run_model(args):
         dist.destroy_process_group()
 
 
-def run_probe(args):
-    """Rates of the access patterns that bound the tensor-core kernels, measured with the kernels' own lane layout
-    (8 lanes x 16 bytes = one 128-byte line, four pseudo-random lines per warp instruction): `scatter` =
-    red.global.add.v4.f32 into an fp32 buffer (the input-gradient epilogue), `gather` = 16-byte read-only loads
-    (the corner fetches).  Buffer sizes: config 2's dX (103 MB) / bf16 input copy (51 MB), and 16 MB for the
-    L2-resident case."""
-    import ctypes
-    from deform_conv3d_pytorch_op_b200 import _lib, build as _build
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    _build.build()
-    lib = ctypes.CDLL(_build.PROBE_LIB)
-    lib.dcn_probe_scatter.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
-    lib.dcn_probe_gather.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
-                                     ctypes.c_void_p]
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    sink = torch.zeros(1, dtype=torch.int32, device=dev)
-    st = _lib.current_stream(dev)
-    out = {}
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    for name, nbytes in (("103MB", 32 * 256 * 56 * 56 * 4), ("51MB", 32 * 256 * 56 * 56 * 2), ("16MB", 16 << 20)):
-        buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=dev)
-        for kind in ("scatter", "gather"):
-            best = 0.0
-            for blocks_per_sm in (1, 2, 4):
-                blocks, reps = sms * blocks_per_sm, 512
-                def launch():
-                    if kind == "scatter":
-                        r = lib.dcn_probe_scatter(buf.data_ptr(), nbytes, blocks, reps, st)
-                    else:
-                        r = lib.dcn_probe_gather(buf.data_ptr(), nbytes, blocks, reps, sink.data_ptr(), st)
-                    assert r == 0, r
-                for _ in range(3):
-                    launch()
-                torch.cuda.synchronize()
-                a, b = ev(), ev()
-                a.record()
-                for _ in range(5):
-                    launch()
-                b.record()
-                torch.cuda.synchronize()
-                gbs = 5.0 * blocks * 512 * reps * 16 / (a.elapsed_time(b) * 1e-3) / 1e9
-                best = max(best, gbs)
-            out["%s_%s_gbs" % (kind, name)] = round(best, 1)
-    print(json.dumps({"probe": out, "sms": sms, "unit": "GB/s of 16-byte pieces, best of 1/2/4 CTAs of 512 threads per SM"}),
-          flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -320,16 +357,12 @@ def main():
                     help="config 5: keep the stock layers in NCDHW instead of channels_last_3d")
     ap.add_argument("--precision", default="auto", choices=["auto", "exact", "bf16"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (0: the configuration's)")
-    ap.add_argument("--ref-samples", type=int, default=8, help="samples per step of the --impl reference arm")
+    ap.add_argument("--ref-samples", type=int, default=0,
+                    help="samples per step of the --impl reference arm (0: the whole per-GPU batch)")
     ap.add_argument("--cpu-baseline-samples", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--probe", action="store_true",
-                    help="measure the two access patterns that bound the kernels (random 128-byte lines: 16-byte "
-                         "vector reductions, 16-byte gathers) and print their rates instead of the bench line")
     args = ap.parse_args()
-    if args.probe:
-        return run_probe(args)
 
     if args.config == 5:
         run_model(args)
@@ -370,8 +403,7 @@ def main():
     launches_per_step = sum(_lib.lib().dcn_launch_count(ctypes.byref(op.p), ps) for ps in (0, 3))
 
     # L2 hygiene: the working set of configs 2-4 is several times the 126 MB L2; for small ones flush.
-    working_set = sum(t.numel() * 4 for t in (x, off, dy)) * 2 + x.numel() * 4
-    flush = working_set < 512 * 1024 * 1024
+    working_set, flush = workload_l2(wl)
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush else None
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -546,45 +578,33 @@ def main():
         t_gs = 3.0 * wl.bytes_gather_scatter() / (peaks["hbm_gbs"] * 1e9)
         roof.update({"gather_scatter": {"bytes_per_pass": wl.bytes_gather_scatter(), "passes": 3,
                                         "t_roof_ms": t_gs * 1e3, "frac": t_gs / (ms_per_step * 1e-3)}})
-        # third reading, for the input-gradient pass only: its fp32 vector reductions against the rate the same
-        # access pattern reaches alone (bench.py --probe, committed under profiles/)
-        ppath = os.path.join(ROOT, "profiles", "access_pattern_probes.json")
-        if os.path.exists(ppath) and prec == "bf16":
-            with open(ppath) as f:
-                pj = json.load(f)
-            ach = wl.bytes_gather_scatter() / (pass_ms["backward_data"] * 1e-3) / 1e9
-            roof["scatter_path"] = {"pass": "backward_data", "bytes": wl.bytes_gather_scatter(), "achieved": ach,
-                                    "peak": pj["scatter_red_v4_gbs"], "unit": "GB/s",
-                                    "frac": ach / pj["scatter_red_v4_gbs"],
-                                    "peak_source": "profiles/access_pattern_probes.json (bench.py --probe)"}
+        # DRAM bytes per launch of the dominant pass's main kernel, from one ncu capture (profiles/: the summary
+        # named for that kernel gives the capture's command, batch and byte counts), scaled by positions
         traffic = None
-        tpath = os.path.join(ROOT, "profiles", "traffic_cfg%d.json" % args.config)
-        if os.path.exists(tpath):            # DRAM bytes of the dominant kernel from the committed ncu capture, scaled
-            with open(tpath) as f:
-                tj = json.load(f)
-            traffic = tj["bytes_per_launch"][dom] * (wl.N * wl.ov) / float(tj["positions"])
+        if prec == "bf16" and (args.config, dom) in NCU_DRAM_BYTES:
+            cap_bytes, cap_positions = NCU_DRAM_BYTES[(args.config, dom)]
+            traffic = cap_bytes * (wl.N * wl.ov) / float(cap_positions)
         roof.update({"kernel": dom, "kernel_ms": pass_ms[dom], "traffic": traffic, "peak_source": peaks["source"],
                      "pass_ms": pass_ms,
                      "whole_step_frac": max(wl.flops() / (peaks["bf16_tflops"] * 1e12),
                                             (fwd_b + bwd_b) / (peaks["hbm_gbs"] * 1e9)) / (ms_per_step * 1e-3)})
         cpu = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:       # a CPU leg only at N = 1 (rank 0)
             from oracle import oracle as orc
             orc.build()
             n = max(1, min(wl.N, args.cpu_baseline_samples))
             cpu_port_run(wl, 1)
             dt = cpu_port_run(wl, n)
-            cpu = {"value": wl.flops(n) / dt / 1e12, "unit": UNIT, "cores": len(os.sched_getaffinity(0)),
-                   "kind": "port", "seconds": dt,
+            cpu = {"value": wl.flops(n) / dt / 1e12, "unit": UNIT, "cores": _host_threads(),
+                   "omp_threads": _omp_threads(), "kind": "port", "seconds": dt,
                    "sample": "%d of %d samples, forward + backward (dX, dOffset, dW), fp32 oracle port" % (n, wl.N)}
+            torch.cuda.empty_cache()
+            cpu["reference_kernels_b200"] = reference_kernels_run(wl, dev)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": wl.name, "per_gpu_batch": wl.N, "precision": prec, "io_dtype": "f32",
-                       "l2": "flushed between steps" if flush else "working set %.0f MB > 126 MB L2" %
-                             (working_set / 1e6),
-                       "parallelism": "batch-sharded x%d, dW all-reduce" % world if world > 1 else "single GPU"},
+            "config": our_config(wl, prec, world, flush, working_set),
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * args.steps,
         }

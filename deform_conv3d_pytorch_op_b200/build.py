@@ -12,9 +12,7 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB = os.path.join(CSRC, "libdcn.so")
-PROBE_LIB = os.path.join(CSRC, "libdcn_probe.so")       # access-pattern probes of bench.py --probe, not the C ABI
 SOURCES = ["dcn_api.cu", "dcn_simt.cu", "dcn_tc.cu"]
-PROBE_SOURCE = "dcn_probe.cu"
 HEADERS = ["dcn_common.cuh", "dcn_internal.h", os.path.join("..", "..", "include", "dcn.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + os.environ.get("DCN_NVCC_EXTRA", "").split()
@@ -28,7 +26,7 @@ def _nvcc() -> str:
 
 
 def is_stale() -> bool:
-    if not os.path.exists(LIB) or not os.path.exists(PROBE_LIB):
+    if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
     deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
@@ -55,8 +53,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if pr.returncode != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     subprocess.check_call([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs)
-    subprocess.check_call([nvcc] + [f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")] +
-                          ["-shared", os.path.join(CSRC, PROBE_SOURCE), "-o", PROBE_LIB])
     return LIB
 
 

@@ -427,13 +427,6 @@ int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const
     return tc_forward(g, ndim, deform, x, off, w, bias, y, ptr, kStaticScratchBytes, st);
 }
 
-#ifdef DCN_PROFILE
-extern "C" int dcn_debug_fwd_profile(unsigned long long* out) {
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out, g_fwd_prof, 32 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -5;
-}
-#endif
-
 int tc_check_status(cudaStream_t st) {
     if (cudaStreamSynchronize(st) != cudaSuccess) return -5;
     unsigned int v = 0;

@@ -17,21 +17,6 @@
 // K chunk is shared by both 128-row halves of the output-channel block.
 #pragma once
 
-// Cycle accounting of the roles (build with -DDCN_PROFILE; read with dcn_debug_fwd_profile): per role the
-// cycles spent in its waits and in total, taken on CTA 0.  Compiled out of the product build.
-#ifdef DCN_PROFILE
-__device__ unsigned long long g_fwd_prof[32];
-#define PROF_DECL long long pw_[4] = {0, 0, 0, 0}; const long long pstart_ = clock64();
-#define PROF_T0 const long long pc0_ = clock64();
-#define PROF_ADD(k) pw_[k] += clock64() - pc0_;
-#define PROF_OUT(role, cond) if (blockIdx.x == 0 && (cond)) { for (int z_ = 0; z_ < 4; ++z_) g_fwd_prof[(role) * 5 + z_] = pw_[z_]; g_fwd_prof[(role) * 5 + 4] = clock64() - pstart_; }
-#else
-#define PROF_DECL
-#define PROF_T0
-#define PROF_ADD(k)
-#define PROF_OUT(role, cond)
-#endif
-
 constexpr int kMaxStages = 4;
 constexpr int kFwdCoordWarps = 4;               // forward: coordinate + epilogue warps, one per tensor-memory lane quarter
 constexpr int fwd_threads(int gw) { return 32 * (2 + kFwdCoordWarps + gw); }
@@ -121,7 +106,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
     if (warp == 0) {
         // ------------------------------------------------ MMA issue
         if (lane == 0) {
-            PROF_DECL
             uint32_t tl = 0;
             Ring rs;
             bool ok = true;
@@ -132,11 +116,11 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 const int mtb = (MT - mb * 2) >= 2 ? 2 : 1;
                 const int kc0 = wi.kc0, kc1 = wi.kc1;
                 const uint32_t b = tl & 1;
-                { PROF_T0 ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1); PROF_ADD(0) }
+                ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
                 tc_fence_after();
                 for (int kc = kc0; kc < kc1 && ok; ++kc, rs.next(n_stages)) {
                     const uint32_t s = rs.i;
-                    { PROF_T0 ok = mbar_wait(&ctl->full[s], rs.ph); PROF_ADD(1) }
+                    ok = mbar_wait(&ctl->full[s], rs.ph);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_base = smem_u32(smem + s * kFwdStageBytes);
@@ -156,7 +140,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 }
                 if (ok) umma_commit(&ctl->acc_full[b]);
             }
-            PROF_OUT(0, true)
         }
     } else if (warp == 1) {
         // ------------------------------------------------ weight loader
@@ -256,7 +239,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         uint32_t etl = 0;               // ... and how many tiles of this CTA came before it
         bool waiting = false;
         long long t0 = 0;
-        PROF_DECL
         while (true) {
             const bool more = cur.t < n_tiles;
             if (!more && et >= n_tiles) break;
@@ -265,7 +247,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             // when the tables of the tile that needs the accumulator's buffer are about to be filled.
             if (et < n_tiles && (!tab_free || cur.tl >= etl + 2) &&
                 mbar_try_wait(&ctl->acc_full[etl & 1], (etl >> 1) & 1)) {
-                PROF_T0
                 waiting = false;
                 tc_fence_after();
                 const uint32_t b = etl & 1;
@@ -332,11 +313,9 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 mbar_arrive_warp(&ctl->acc_empty[b]);
                 et += gridDim.x;
                 ++etl;
-                PROF_ADD(0)
                 continue;
             }
             if (tab_free) {
-                PROF_T0
                 waiting = false;
                 cp_async_wait<1>();             // this stage's offsets have landed; the next stage's may be in flight
                 const uint32_t tb = rt.i;
@@ -366,7 +345,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                     prefetch(pre, it & 1u);
                 }
                 ++it;
-                PROF_ADD(1)
                 continue;
             }
             // nothing to do yet: bounded wait for either event
@@ -380,7 +358,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             }
         }
         cp_async_wait<0>();
-        PROF_OUT(1, warp == 2 && lane == 0)
     } else {
         // ------------------------------------------------ gather warps
         // Within a thread a stage is produced in passes of RPP rows; where the registers allow it the loads
@@ -407,7 +384,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         int ckc = 0, ckc_end = 0, ch = 0, cj = 0, cc = 0, csl = 0;
         Ring rtab, rstg;            // table buffer and operand stage of the issue cursor
         bool failed = false;
-        PROF_DECL
         const uint32_t tab_s = smem_u32(tab);
         const uint32_t pix_bytes = (uint32_t)g.C * 2u;
         const __nv_bfloat16* xbase[RT];         // channels-last base of the sample of each of this thread's rows
@@ -438,7 +414,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
             if (ct >= n_tiles || failed) return false;
             const uint32_t tb = rtab.i;
             if (ch == 0) {
-                { PROF_T0 const bool okw = mbar_wait(&ctl->tab_full[tb], rtab.ph); PROF_ADD(0) if (!okw) { failed = true; return false; } }
+                const bool okw = mbar_wait(&ctl->tab_full[tb], rtab.ph); if (!okw) { failed = true; return false; }
                 csl = ctl->slot_of_chunk[tb][chunk];
                 const int kp = ckc * kTileK + chunk * 8;
                 uint32_t tap, cl;
@@ -470,7 +446,7 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
         auto finish = [&](Pass& p) -> bool {
             const uint32_t s = p.s;
             if (p.h == 0) {
-                { PROF_T0 const bool okw = mbar_wait(&ctl->empty[s], p.ph ^ 1u); PROF_ADD(1) if (!okw) { failed = true; return false; } }
+                const bool okw = mbar_wait(&ctl->empty[s], p.ph ^ 1u); if (!okw) { failed = true; return false; }
             }
             const uint32_t b_base = smem_u32(smem + s * kFwdStageBytes + 2 * kTileBytes);
 #pragma unroll
@@ -500,7 +476,6 @@ tc_forward_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const flo
                 if (!finish(pa)) break;
             }
         }
-        PROF_OUT(2, gtid == 0)
     }
 
     // teardown: every role has left its loop (normally or after a bounded wait gave up)

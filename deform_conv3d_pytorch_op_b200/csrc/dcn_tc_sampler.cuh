@@ -64,47 +64,8 @@ __device__ __forceinline__ int slot_key(const SlotInfo& si, int sl) {
     return __shfl_sync(0xffffffffu, si.my_key, col);
 }
 
-// Coordinate-warp side: fill one table entry.
-template <int D, bool DEFORM>
-__device__ __forceinline__ void fill_entry(const Geom& g, const float* __restrict__ off, const OutPos& op, bool pos_ok,
-                                           int key, TabEntry<D, DEFORM>* e) {
-    if constexpr (DEFORM) {
-        int4* ei = reinterpret_cast<int4*>(e->idx);
-        float4* ew = reinterpret_cast<float4*>(e->w);
-        Pt<float, D> s;
-        s.valid = false;
-        if (pos_ok && key >= 0) {
-            uint32_t grp_, tap_;
-            g.d_kv.divmod((uint32_t)key, grp_, tap_);
-            const int grp = (int)grp_, tap = (int)tap_;
-            locate<float, D>(g, off + (size_t)op.n * g.dg * g.kv * D * g.ov, grp, tap, op, s);
-        }
-        int idx[1 << D];
-        float cw[1 << D];
-        if (s.valid) {
-            corner_indices<float, D>(g, s, idx);
-            corner_weights<float, D>(s, cw);
-        } else {
-#pragma unroll
-            for (int i = 0; i < (1 << D); ++i) { idx[i] = -1; cw[i] = 0.f; }
-        }
-#pragma unroll
-        for (int q = 0; q < (1 << D) / 4; ++q) {
-            ei[q] = make_int4(idx[4 * q], idx[4 * q + 1], idx[4 * q + 2], idx[4 * q + 3]);
-            ew[q] = make_float4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
-        }
-    } else {
-        int pidx = -1;
-        if (pos_ok && key >= 0) {
-            const int tap = (int)((uint32_t)key - g.d_kv.div((uint32_t)key) * (uint32_t)g.kv);
-            int t;
-            if (locate_plain<D>(g, tap, op, t)) pidx = t;
-        }
-        *reinterpret_cast<int4*>(e->idx) = make_int4(pidx, 0, 0, 0);
-    }
-}
-
-// Same, with the D offset values already at hand (prefetched into shared memory).
+// Coordinate-warp side: fill one table entry from the D offset values of its point (prefetched into shared
+// memory).
 template <int D, bool DEFORM>
 __device__ __forceinline__ void fill_entry_from(const Geom& g, const float (&offv)[D], const OutPos& op, bool pos_ok,
                                                 int key, TabEntry<D, DEFORM>* e) {
@@ -165,80 +126,7 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
     return d;
 }
 
-// Gather-warp side, step 1: issue the corner loads of one entry (8 channels starting at xn).
-template <int D, bool DEFORM>
-__device__ __forceinline__ void gather_issue(const TabEntry<D, DEFORM>& e, const __nv_bfloat16* __restrict__ xn,
-                                             int C, uint4 (&q)[DEFORM ? (1 << D) : 1]) {
-    if (e.idx[0] < 0) {
-#pragma unroll
-        for (int i = 0; i < (DEFORM ? (1 << D) : 1); ++i) q[i] = make_uint4(0, 0, 0, 0);
-        return;
-    }
-#pragma unroll
-    for (int i = 0; i < (DEFORM ? (1 << D) : 1); ++i)
-        q[i] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)e.idx[i] * C));
-}
-
-// step 2: interpolate and round to 8 bf16.
-template <int D, bool DEFORM>
-__device__ __forceinline__ uint4 gather_finish(const TabEntry<D, DEFORM>& e, const uint4 (&q)[DEFORM ? (1 << D) : 1]) {
-    if constexpr (!DEFORM) return q[0];
-    else {
-        if (e.idx[0] < 0) return make_uint4(0, 0, 0, 0);
-        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-        for (int c = 0; c < (1 << D); ++c) {
-            const uint64_t w2 = pack_f32x2(e.w[c], e.w[c]);
-            const uint32_t wd[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                acc[i] = ffma2(w2, pack_f32x2(bf16_lo(wd[i]), bf16_hi(wd[i])), acc[i]);
-        }
-        uint32_t out[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float lo, hi;
-            unpack_f32x2(acc[i], lo, hi);
-            out[i] = pack_bf16x2(lo, hi);
-        }
-        return make_uint4(out[0], out[1], out[2], out[3]);
-    }
-}
-
-// Pipelined form: issue keeps only the loaded vectors and the weights; an invalid entry yields zero weights and
-// zero vectors, so the later interpolation returns exactly zero without a flag.
-template <int D, bool DEFORM>
-__device__ __forceinline__ void gather_issue_w(const TabEntry<D, DEFORM>* ep, const __nv_bfloat16* __restrict__ xn,
-                                               int C, uint4 (&q)[DEFORM ? (1 << D) : 1],
-                                               float (&w)[DEFORM ? (1 << D) : 1]) {
-    constexpr int NQ = DEFORM ? (1 << D) : 1;
-    const int4* ei = reinterpret_cast<const int4*>(ep->idx);
-    int idx[DEFORM ? (1 << D) : 4];
-#pragma unroll
-    for (int i = 0; i < (DEFORM ? (1 << D) : 4) / 4; ++i) {
-        const int4 t = ei[i];
-        idx[4 * i] = t.x; idx[4 * i + 1] = t.y; idx[4 * i + 2] = t.z; idx[4 * i + 3] = t.w;
-    }
-    if constexpr (DEFORM) {
-        const float4* ew = reinterpret_cast<const float4*>(ep->w);
-#pragma unroll
-        for (int i = 0; i < NQ / 4; ++i) {
-            const float4 t = ew[i];
-            w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
-        }
-    } else {
-        w[0] = 1.f;
-    }
-    if (idx[0] < 0) {
-#pragma unroll
-        for (int i = 0; i < NQ; ++i) q[i] = make_uint4(0, 0, 0, 0);
-    } else {
-#pragma unroll
-        for (int i = 0; i < NQ; ++i) q[i] = __ldg(reinterpret_cast<const uint4*>(xn + (size_t)idx[i] * C));
-    }
-}
-
-// Lean form of gather_issue_w: the entry at shared address `entry_s`, the 8 channels at `xrow` (sample base +
+// Gather-warp side, step 1: issue the corner loads of one entry.  The entry at shared address `entry_s`, the 8 channels at `xrow` (sample base +
 // channel), `pix_bytes` = bytes between consecutive input positions of the channels-last copy.  Loads of an
 // invalid entry are predicated off (no divergent branch); its weights are zero.
 template <int D, bool DEFORM>
@@ -294,14 +182,4 @@ __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 <<
         }
         return make_uint4(out[0], out[1], out[2], out[3]);
     }
-}
-
-template <int D, bool DEFORM>
-__device__ __forceinline__ TabEntry<D, DEFORM> load_entry(const TabEntry<D, DEFORM>* p) {
-    TabEntry<D, DEFORM> e;
-    const int4* s = reinterpret_cast<const int4*>(p);
-    int4* d = reinterpret_cast<int4*>(&e);
-#pragma unroll
-    for (int i = 0; i < (int)(sizeof(TabEntry<D, DEFORM>) / 16); ++i) d[i] = s[i];
-    return e;
 }

@@ -60,4 +60,6 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "reference_vectors.npz"))
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <output .npz path>")
+    main(sys.argv[1])

@@ -51,18 +51,24 @@ def run_oracle(case, tensors, dtype=None, oob=True):
     return out
 
 
-def lattice_mask(case, off_np, tol=1e-5):
-    """True where some coordinate of the sampling point lies within tol of the integer lattice (there the
-    offset derivative is one-sided and fp32 / fp64 coordinates may pick different sides).  Shape of doff."""
+def lattice_mask(case, off_np, tol=1e-6):
+    """True where the offset derivative is one-sided and the fp32 and float64 evaluations may legitimately pick
+    different sides: some coordinate of the sampling point lies within tol of the integer lattice, or the
+    fp32 coordinate (one rounding of base + offset) selects other corners than the float64 one.  Shape of doff."""
     p = case.problem()
     N = off_np.shape[0]
     p.N = N
     mask = np.zeros(off_np.shape, dtype=bool)
     nd = case.ndim
     for n in range(N):
-        pts, valid, lo, hi = orc.dump_points(p, np.ascontiguousarray(off_np[n].astype(np.float32)))
-        frac = np.abs(pts - np.round(pts))
+        o32 = np.ascontiguousarray(off_np[n].astype(np.float32))
+        pts, valid, lo, hi = orc.dump_points(p, o32)
+        pts64, valid64, lo64, hi64 = orc.dump_points(p, o32.astype(np.float64))
+        frac = np.abs(pts64 - np.round(pts64))
         near = (frac < tol).any(axis=-1)            # [dg, kv, ov]
+        near |= (valid != valid64)
+        both = (valid != 0) & (valid64 != 0)
+        near |= both & ((lo != lo64).any(axis=-1) | (hi != hi64).any(axis=-1))
         near = np.repeat(near[:, :, None, :], nd, axis=2).reshape((-1,) + tuple(p.out_size))
         mask[n] = near
     return mask

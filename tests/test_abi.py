@@ -23,23 +23,10 @@ def test_header_symbols_are_exported(L):
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     declared = set(re.findall(r"\b(dcn_[a-z0-9_]+)\s*\(", text))
     assert len(declared) >= 20
-    assert declared == set(_lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS + [s for s in declared if s not in
-                                                                        _lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS])
+    # the header and the binding list the same entry points, and the library exports each of them
+    assert declared == set(_lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS)
     for sym in sorted(declared):
         assert hasattr(L, sym), sym
-    for sym in _lib.GENERIC_SYMBOLS + _lib.LEGACY_SYMBOLS:
-        assert sym in declared, sym
-
-
-def test_probe_library_is_separate_from_the_abi(L):
-    """bench.py --probe uses two access-pattern kernels; they live in their own library, not in libdcn.so."""
-    import ctypes
-    from deform_conv3d_pytorch_op_b200 import build
-    build.build()
-    probe = ctypes.CDLL(build.PROBE_LIB)
-    for sym in ("dcn_probe_scatter", "dcn_probe_gather"):
-        assert hasattr(probe, sym), sym
-        assert not hasattr(L, sym), sym
 
 
 def test_channels_last_is_a_bf16_option(L):
