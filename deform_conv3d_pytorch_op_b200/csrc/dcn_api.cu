@@ -131,10 +131,10 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
 int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
     if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_BACKWARD ? 2 : 1;
-    if (pass == DCN_PASS_BACKWARD) return p->channels_last ? 6 : 7;   // input copy, dy pack, weight pack, dgrad, (dx transpose,) wgrad, dW unpack
     Geom g;
     make_geom(p, g);
-    return dcn::tc_launch_count(g, p->ndim, pass);
+    if (!dcn::tc_supported(g, p->ndim, p->deformable)) return 0;
+    return dcn::tc_launch_count(g, p->ndim, p->deformable, pass);
 }
 
 int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const void* weight, const void* bias,
@@ -274,6 +274,21 @@ int dcn_debug_points(const dcn_problem* p, const void* offset, int32_t n, void* 
     Geom g;
     make_geom(p, g);
     return dcn::debug_points(g, p->dtype, p->ndim, offset, n, coords, valid, lo, hi, static_cast<cudaStream_t>(stream));
+}
+
+int dcn_debug_tc_points(const dcn_problem* p, const void* offset, int32_t n, void* coords, int32_t* valid,
+                        int32_t* lo, int32_t* hi, void* ws, size_t ws_bytes, void* stream) {
+    const int v = validate(p);
+    if (v != DCN_OK) return v;
+    if (!p->deformable || p->precision != DCN_PREC_BF16) return DCN_ERR_UNSUPPORTED;
+    if (offset == nullptr || coords == nullptr || valid == nullptr || lo == nullptr || hi == nullptr) return DCN_ERR_NULL;
+    if (n < 0 || n >= p->N) return DCN_ERR_SHAPE;
+    Geom g;
+    make_geom(p, g);
+    if (!dcn::tc_supported(g, p->ndim, p->deformable)) return DCN_ERR_UNSUPPORTED;
+    if (!workspace_ok(ws, ws_bytes, dcn::tc_backward_workspace_bytes(g))) return DCN_ERR_WORKSPACE;
+    return dcn::tc_debug_points(g, p->ndim, p->deformable, (const float*)offset, n, (float*)coords, valid, lo, hi, ws,
+                                ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int dcn_check_status(void* stream) { return dcn::tc_check_status(static_cast<cudaStream_t>(stream)); }

@@ -14,6 +14,8 @@
 //   dx_cl  [N][in volume][C] fp32      channels-last input-gradient accumulator (backward data)
 //
 // Requirements (dcn_precision_supported): fp32 tensors, C/G and C/dg multiples of 8.
+#include <stdlib.h>
+
 #include "dcn_internal.h"
 #include "dcn_tc_common.cuh"
 
@@ -199,6 +201,7 @@ int launch_channels_last(const Geom& g, const float* x, __nv_bfloat16* xcl, cuda
 #include "dcn_tc_wgrad2.cuh"
 #include "dcn_tc_dgrad.cuh"
 #include "dcn_tc_dgrad2.cuh"
+#include "dcn_tc_bwd2d.cuh"
 
 struct BwdWeightWorkspace {
     size_t xcl_off, dpk_off, dwpk_off, total;
@@ -214,7 +217,7 @@ BwdWeightWorkspace bwd_weight_workspace(const Geom& g) {
 }
 
 struct BwdDataWorkspace {
-    size_t xcl_off, dpk_off, wpk_off, dxcl_off, dxcl_bytes, dwpk_off, total;      // dwpk: fused backward only
+    size_t xcl_off, dpk_off, wpk_off, scale_off, dxcl_off, dxcl_bytes, dwpk_off, total;   // dwpk: fused backward only
 };
 BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     const DgDims d = dg_dims(g);
@@ -222,11 +225,45 @@ BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     w.xcl_off = 0;
     w.dpk_off = align_up((size_t)g.N * g.iv * g.C * 2, 256);
     w.wpk_off = w.dpk_off + align_up((size_t)g.G * d.MT * d.PC2 * kTileBytes, 256);
-    w.dxcl_off = w.wpk_off + align_up((size_t)g.G * d.NB * d.OC * 2 * kTileBytes, 256);
+    size_t wpk_bytes = (size_t)g.G * d.NB * d.OC * 2 * kTileBytes;
+    if (g.Cg % 8 == 0 && b2_wpk_bytes(g) > wpk_bytes) wpk_bytes = b2_wpk_bytes(g);   // slab-wise tiles of dcn_tc_bwd2d.cuh
+    w.scale_off = w.wpk_off + align_up(wpk_bytes, 256);
+    w.dxcl_off = w.scale_off + 256;                    // two words: bit patterns of max|dy| and max|W|
     w.dxcl_bytes = align_up((size_t)g.N * g.iv * g.C * 4, 256);
+    // the shared-memory-accumulating kernel has no channels-last dX scratch; its sampling-point entries live there
+    if (g.Cg % 8 == 0 && b2_points_bytes(g) > w.dxcl_bytes) w.dxcl_bytes = align_up(b2_points_bytes(g), 256);
     w.dwpk_off = w.dxcl_off + w.dxcl_bytes;
     w.total = w.dwpk_off + align_up(dwpk_bytes(g), 256);
     return w;
+}
+
+// The shared-memory-accumulating backward-data kernel is taken whenever it fits (DCN_BWD2D=0 forces the
+// global-reduction kernels, for A/B measurements).
+bool use_bwd2d(const Geom& g, int ndim, int deform) {
+    static const bool off = [] { const char* e = getenv("DCN_BWD2D"); return e != nullptr && e[0] == '0'; }();
+    return !off && b2_supported(g, ndim, deform);
+}
+
+// dy packed (max|dy| taken on the way), slab-wise weight tiles (max|W|), cleared dOffset, then the kernel.
+int run_bwd2d(const Geom& g, const __nv_bfloat16* xcl, const float* off, const float* w, const float* dy, uint8_t* dpk,
+              uint8_t* wpk, unsigned int* scale, uint4* pts, float* dx, float* doff, bool accumulate, cudaStream_t st) {
+    const B2Dims d = b2_dims(g);
+    {
+        const long long total = (long long)g.N * g.dg * g.kv * g.ov;
+        const long long want = (total + 255) / 256;
+        const int blocks = (int)(want < 16ll * sm_count() ? want : 16ll * sm_count());
+        b2_points_kernel<<<blocks, 256, 0, st>>>(g, off, pts, d.Wp, d.W2);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+    }
+    if (cudaMemsetAsync(scale, 0, 8, st) != cudaSuccess) return -5;
+    int r = launch_pack_dy(g, dy, dpk, d.MT, d.PC, st, scale);
+    if (r != 0) return r;
+    pack_weight_slab<<<g.G * d.SL * d.OC, 256, 0, st>>>(g, w, wpk, d.SL, d.OC, scale + 1);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (doff != nullptr &&
+        cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * 2 * g.ov * sizeof(float), st) != cudaSuccess)
+        return -5;
+    return launch_tc_bwd2d(g, xcl, pts, dpk, wpk, scale, dx, doff, accumulate, st);
 }
 
 }  // namespace
@@ -246,11 +283,34 @@ size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
     return bwd_weight_workspace(g).total;
 }
 
-int tc_launch_count(const Geom& g, int ndim, int pass) {
-    (void)ndim;
+// Kernels a pass enqueues when every gradient is wanted (memsets not counted).
+int tc_launch_count(const Geom& g, int ndim, int deform, int pass) {
+    const bool b2 = use_bwd2d(g, ndim, deform);
     if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
-    if (pass == 1) return g.cl ? 4 : 5;   // input copy, dy pack, weight pack, implicit GEMM + scatter, (dx transpose-add)
-    return 4;                     // channels-last copy, dy pack, implicit GEMM, dW unpack
+    if (pass == 1) {
+        if (b2) return 5;         // input copy, sampling points, dy pack, slab weight pack, GEMM + shared-memory scatter
+        return g.cl ? 4 : 5;      // input copy, dy pack, weight pack, implicit GEMM + scatter, (dx transpose-add)
+    }
+    if (pass == 2) return 4;      // channels-last copy, dy pack, implicit GEMM, dW unpack
+    // fused backward (input copy taken over from the forward pass when the caller hands it in: counted here)
+    if (b2) return 7;             // input copy, sampling points, dy pack, slab weight pack, dgrad, wgrad, dW unpack
+    return g.cl ? 6 : 7;          // input copy, dy pack, weight pack, dgrad, (dx transpose,) wgrad, dW unpack
+}
+
+int tc_debug_points(const Geom& g, int ndim, int deform, const float* off, int n, float* coords, int32_t* valid,
+                    int32_t* lo, int32_t* hi, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!b2_supported(g, ndim, deform)) return -3;
+    const BwdDataWorkspace l = bwd_data_workspace(g);
+    if (ws_bytes < l.total) return -4;
+    uint4* pts = reinterpret_cast<uint4*>(static_cast<uint8_t*>(ws) + l.dxcl_off);
+    const B2Dims d = b2_dims(g);
+    const long long total = (long long)g.N * g.dg * g.kv * g.ov;
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 16ll * sm_count() ? want : 16ll * sm_count());
+    b2_points_kernel<<<blocks, 256, 0, st>>>(g, off, pts, d.Wp, d.W2);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    b2_points_decode_kernel<<<blocks, 256, 0, st>>>(g, pts, n, d.Wp, d.W2, coords, valid, lo, hi);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
@@ -289,6 +349,9 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
         r = launch_channels_last(g, x, xcl, st);
         if (r != 0) return r;
     }
+    if (use_bwd2d(g, ndim, deform))
+        return run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<unsigned int*>(base + l.scale_off),
+                         reinterpret_cast<uint4*>(base + l.dxcl_off), dx, doff, true, st);
     r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
     if (r != 0) return r;
     pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
@@ -362,9 +425,16 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         if (r != 0) return r;
         xcl = mine;
     }
-    r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
-    if (r != 0) return r;
-    if (dx != nullptr || doff != nullptr) {
+    const bool b2 = (dx != nullptr || doff != nullptr) && use_bwd2d(g, ndim, deform);
+    if (b2) {
+        r = run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<unsigned int*>(base + l.scale_off),
+                      reinterpret_cast<uint4*>(base + l.dxcl_off), dx, doff, false, st);
+        if (r != 0) return r;
+    } else {
+        r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
+        if (r != 0) return r;
+    }
+    if (!b2 && (dx != nullptr || doff != nullptr)) {
         pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
         if (cudaGetLastError() != cudaSuccess) return -5;
         if (dxcl != nullptr && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;

@@ -25,8 +25,10 @@ struct WgSmem {
 
 // dy [N, O, ov] fp32 -> bf16 tiles [G][MT][PC][128 o rows x 64 positions], swizzled; rows >= Og and
 // positions >= P are zero.  Used by both backward kernels.
+// If absmax_bits is not null it is raised to the bit pattern of max|dy| (non-negative floats order like their bits).
 __global__ void __launch_bounds__(256)
-pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, int MT, long long PC) {
+pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, int MT, long long PC,
+        unsigned int* __restrict__ absmax_bits) {
     const long long pc = blockIdx.x;
     const int mt = blockIdx.y % MT, j = blockIdx.y / MT;
     uint8_t* dst = dpk + (((size_t)j * MT + mt) * PC + pc) * kTileBytes;
@@ -37,6 +39,7 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
     const bool ok0 = P0 < g.P, ok1 = P0 + 1 < g.P;
     if (ok0) g.d_ov.divmod((uint32_t)P0, n0, op0);
     if (ok1) g.d_ov.divmod((uint32_t)(P0 + 1), n1, op1);
+    float mx = 0.f;
     for (int row = wrp; row < 128; row += 8) {      // (forcing this loop to unroll 8-fold measured 20 % slower)
         const int ol = mt * 128 + row;
         float a = 0.f, b = 0.f;
@@ -45,8 +48,18 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
             if (ok0) a = __ldg(dy + ((size_t)n0 * g.O + o) * g.ov + op0);
             if (ok1) b = __ldg(dy + ((size_t)n1 * g.O + o) * g.ov + op1);
         }
+        mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
         const uint32_t chunk = lane / 4;            // 8 positions per 16-byte chunk
         *reinterpret_cast<uint32_t*>(dst + swz_offset(row, chunk) + (lane % 4) * 4) = pack_bf16x2(a, b);
+    }
+    if (absmax_bits != nullptr) {
+        __shared__ unsigned int blk_max;
+        if (threadIdx.x == 0) blk_max = 0u;
+        __syncthreads();
+        const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(mx));
+        if (lane == 0 && m != 0) atomicMax(&blk_max, m);
+        __syncthreads();
+        if (threadIdx.x == 0 && blk_max != 0) atomicMax(absmax_bits, blk_max);
     }
 }
 
@@ -71,10 +84,11 @@ pack_dy_cl(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk
     }
 }
 
-inline int launch_pack_dy(const Geom& g, const float* dy, uint8_t* dpk, int MT, long long PC, cudaStream_t st) {
+inline int launch_pack_dy(const Geom& g, const float* dy, uint8_t* dpk, int MT, long long PC, cudaStream_t st,
+                          unsigned int* absmax_bits = nullptr) {
     const dim3 grid((unsigned)PC, (unsigned)(g.G * MT));
     if (g.cl) pack_dy_cl<<<grid, 256, 0, st>>>(g, dy, dpk, MT, PC);
-    else pack_dy<<<grid, 256, 0, st>>>(g, dy, dpk, MT, PC);
+    else pack_dy<<<grid, 256, 0, st>>>(g, dy, dpk, MT, PC, absmax_bits);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -215,6 +215,25 @@ class Op:
         _lib.check(st, "dcn_backward_weight")
         return dw, db
 
+    def debug_tc_points(self, offset: torch.Tensor, n: int):
+        """Coordinates / validity / corner indices of sample ``n`` decoded from the sampling-point entries that the
+        tensor-core backward-data kernel of the 2-D deformable operator consumes (bf16 precision)."""
+        offset = _prep(offset, "offset")
+        dg, kv, ov = self.C // self.p.cpg, self.offset_channels // (self.C // self.p.cpg) // self.ndim, 1
+        for s in self.out_size:
+            ov *= s
+        coords = torch.empty((dg, kv, ov, self.ndim), dtype=offset.dtype, device=offset.device)
+        valid = torch.empty((dg, kv, ov), dtype=torch.int32, device=offset.device)
+        lo = torch.empty((dg, kv, ov, self.ndim), dtype=torch.int32, device=offset.device)
+        hi = torch.empty_like(lo)
+        ws, nb = self._ws(_lib.PASS_BACKWARD)
+        with torch.cuda.device(offset.device):
+            st = _lib.lib().dcn_debug_tc_points(ctypes.byref(self.p), _lib.ptr(offset), n, _lib.ptr(coords),
+                                                _lib.ptr(valid), _lib.ptr(lo), _lib.ptr(hi), _lib.ptr(ws), nb,
+                                                _lib.current_stream(offset.device))
+        _lib.check(st, "dcn_debug_tc_points")
+        return coords, valid, lo, hi
+
     def debug_points(self, offset: torch.Tensor, n: int):
         """Coordinates / validity / corner indices of sample ``n`` as the device routine computes them."""
         offset = _prep(offset, "offset")

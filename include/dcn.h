@@ -15,8 +15,10 @@
  *     NC(L)HW storage on the current device; `stream` is a cudaStream_t passed as void*;
  *   - nothing is allocated, nothing synchronises: work is enqueued on `stream` and the call
  *     returns; the caller owns every buffer including the workspace;
- *   - re-entrant and thread-safe (no global state; inputs are never modified, unlike the
- *     reference launchers, which temporarily reshape `weight`);
+ *   - re-entrant and thread-safe: inputs are never modified (the reference launchers temporarily
+ *     reshape `weight`) and the library keeps no state between calls, with two exceptions that
+ *     are process-wide per device: the sticky status word read by dcn_check_status, and the fixed
+ *     scratch array of dcn_forward_static_scratch (calls of that entry point must be serialised);
  *   - the generic dcn_* functions return DCN_OK (0) or a negative dcn_status; the
  *     reference-named wrappers at the bottom return 1 on success like the functions they
  *     replace, and a negative dcn_status where the reference would have raised THError.
@@ -156,6 +158,15 @@ int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const 
  * computed by the same device routine the kernels use. */
 int dcn_debug_points(const dcn_problem* p, const void* offset, int32_t n, void* coords, int32_t* valid,
                      int32_t* lo, int32_t* hi, void* stream);
+
+/* Same outputs as dcn_debug_points, taken from the sampling-point entries the tensor-core backward-data kernel
+ * of the 2-D deformable operator consumes: the entry pre-pass runs over the whole batch into `workspace`
+ * (dcn_workspace_bytes(p, DCN_PASS_BACKWARD) bytes, where the backward pass keeps them) and sample n's entries are
+ * decoded (corner indices, validity, coordinate = low corner + fraction; valid = -1 flags an entry whose two
+ * encodings of the low corner disagree).  DCN_ERR_UNSUPPORTED where that kernel does not take the problem
+ * (3-D, more than 16 taps, planes too large for shared memory).  fp32 tensors, precision BF16. */
+int dcn_debug_tc_points(const dcn_problem* p, const void* offset, int32_t n, void* coords, int32_t* valid,
+                        int32_t* lo, int32_t* hi, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Reads and clears the sticky device-side status word of the tensor-core kernels (bounded waits that
  * gave up).  Synchronises `stream`.  DCN_OK or DCN_ERR_TIMEOUT. */

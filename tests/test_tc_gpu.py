@@ -121,3 +121,70 @@ def test_channels_last_needs_the_bf16_path():
     y = op.forward(x, off, w, None)
     ref = torch.nn.functional.conv2d(x.cpu().double(), w.cpu().double(), None, padding=1)      # zero offsets
     assert cases.rel_err(y.cpu().numpy(), ref.numpy()) <= 1e-4
+
+
+# ---- shared-memory-accumulating backward-data kernel of the 2-D deformable operator ---------------------------
+_B2_CASES = ["tc2_small", "tc2_dg_groups", "tc2_c256", "tc2_stride_dil", "tc2_cpg16_tiles", "tc2_c128_tail"]
+
+
+@pytest.mark.parametrize("name", _B2_CASES + ["cfg1", "cfg2_sample"])
+def test_tensor_core_point_entries_bit_exact(name):
+    """The sampling-point entries that the tensor-core backward-data kernel consumes (located by its own pre-pass:
+    validity, low / high corner, fractions) against the fp32 oracle: corner indices and validity equal, and the
+    coordinate rebuilt from the entry (low corner + fraction, exact) equal bit for bit."""
+    import dataclasses
+    import deform_conv3d_pytorch_op_b200 as dcn
+    from oracle import oracle as orc
+    if name == "cfg1":
+        case = cases.BASELINE[1]
+    elif name == "cfg2_sample":
+        case = dataclasses.replace(cases.BASELINE[2], N=2)
+    else:
+        case = {c.name: c for c in cases.TC_CASES}[name]
+    x, w, off, dy, b = cases.make_inputs(case)
+    op = dcn.Op(x.cuda(), w.cuda(), case.stride, case.pad, case.dil, case.cpg, case.G, precision="bf16")
+    p = case.problem()
+    offd = off.cuda()
+    for n in range(case.N):
+        coords, valid, lo, hi = [t.cpu().numpy() for t in op.debug_tc_points(offd, n)]
+        rc, rv, rlo, rhi = orc.dump_points(p, np.ascontiguousarray(off[n].numpy()))
+        assert np.array_equal(valid, rv)                 # also: no entry with inconsistent encodings (-1)
+        ok = rv != 0
+        assert np.array_equal(lo[ok], rlo[ok]) and np.array_equal(hi[ok], rhi[ok])
+        assert np.array_equal(coords[ok].view(np.uint32), rc[ok].view(np.uint32))
+        assert (lo[~ok] == -1).all() and (hi[~ok] == -1).all()
+    _check_status()
+
+
+def test_fixed_point_plane_budget_and_early_spill():
+    """Worst case for the fixed-point dX plane: constant dy and weight (every col value sits at the bound the scale
+    is chosen from) and offsets that send EVERY sample of EVERY tap to the same input pixel.  The magnitude budget
+    runs out, the kernel switches to additions that look at the element they found, and the element crosses 2^30
+    and is flushed to dX early -- the result must still be the oracle's."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    from oracle import oracle as orc
+    # one term is 2^18 fixed-point steps here (scale 2^13 x col 32 x weight 1): 24 * 24 * 9 = 5184 of them on one
+    # element pass 2^30, and the budget (2^30 over all elements) is spent after an eighth of the sample
+    N, C, O, H, W = 1, 8, 32, 24, 24
+    case = cases.Case("b2_spill", 2, N, C, O, (H, W), (3, 3), (1, 1), (1, 1), (1, 1), 1, 8)
+    p = case.problem()
+    x = torch.rand(N, C, H, W) * 2 - 1
+    w = torch.ones(O, C, 3, 3)
+    dy = torch.ones(N, O, H, W)
+    off = torch.zeros(N, 18, H, W)
+    th, tw = 5.0, 9.0
+    hh, ww = torch.meshgrid(torch.arange(H, dtype=torch.float32), torch.arange(W, dtype=torch.float32), indexing="ij")
+    for tap in range(9):
+        kh, kw = tap // 3, tap % 3
+        off[0, tap * 2] = th - (hh - 1 + kh)
+        off[0, tap * 2 + 1] = tw - (ww - 1 + kw)
+    xd, wd, od, dyd = x.cuda(), w.cuda(), off.cuda(), dy.cuda()
+    op = dcn.Op(xd, wd, case.stride, case.pad, case.dil, case.cpg, case.G, precision="bf16")
+    dx, doff, dw, _ = op.backward(xd, od, wd, dyd, True, True, True, False, None)
+    dx_s, _ = op.backward_data(xd, od, wd, dyd)
+    _check_status()
+    dx_ref, _ = orc.backward_data(p, x.numpy().astype(np.float64), off.numpy().astype(np.float64),
+                                  w.numpy().astype(np.float64), dy.numpy().astype(np.float64))
+    assert dx_ref[0, 0, 5, 9] == H * W * 9 * O          # all 5184 samples of a channel land on one pixel
+    assert cases.rel_err(dx.cpu().numpy(), dx_ref) <= 1e-5
+    assert cases.rel_err(dx_s.cpu().numpy(), dx_ref) <= 1e-5
