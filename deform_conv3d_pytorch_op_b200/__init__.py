@@ -8,10 +8,10 @@ from ._lib import DcnError, LIB_PATH
 from .functions import Conv2dFunction, ConvOffset2dFunction, ConvOffset3dFunction, LegacyConvOffset2dFunction
 from .modules import Conv2d, ConvOffset2d, ConvOffset3d, DeformConv2d, DeformConv3d, LegacyConvOffset2d
 from .legacy_ops import conv2d_op, deform_conv2d_double_op, deform_conv2d_op, deform_conv3d_op
-from .ops import Op
+from .ops import Op, check_status
 
 __all__ = [
-    "DcnError", "LIB_PATH", "Op",
+    "DcnError", "LIB_PATH", "Op", "check_status",
     "ConvOffset3dFunction", "ConvOffset2dFunction", "Conv2dFunction", "LegacyConvOffset2dFunction",
     "ConvOffset3d", "ConvOffset2d", "Conv2d", "DeformConv3d", "DeformConv2d", "LegacyConvOffset2d",
     "deform_conv3d_op", "deform_conv2d_op", "deform_conv2d_double_op", "conv2d_op",

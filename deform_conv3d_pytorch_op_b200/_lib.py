@@ -41,7 +41,7 @@ _lib: Optional[ctypes.CDLL] = None
 GENERIC_SYMBOLS = [
     "dcn_version", "dcn_status_string", "dcn_output_size", "dcn_validate", "dcn_precision_supported",
     "dcn_workspace_bytes", "dcn_launch_count", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_backward", "dcn_debug_points",
-    "dcn_debug_tc_points",
+    "dcn_debug_tc_points", "dcn_debug_expire_wait",
     "dcn_check_status", "dcn_static_scratch_bytes", "dcn_forward_static_scratch",
 ]
 LEGACY_SYMBOLS = [
@@ -80,6 +80,7 @@ def lib() -> ctypes.CDLL:
         L.dcn_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_debug_points.argtypes = [pp, vp, ctypes.c_int32, vp, vp, vp, vp, vp]
         L.dcn_debug_tc_points.argtypes = [pp, vp, ctypes.c_int32, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
+        L.dcn_debug_expire_wait.argtypes = [vp, vp]
         L.dcn_check_status.argtypes = [vp]
         L.dcn_static_scratch_bytes.restype = ctypes.c_size_t
         L.dcn_forward_static_scratch.argtypes = [pp, vp, vp, vp, vp, vp, vp]

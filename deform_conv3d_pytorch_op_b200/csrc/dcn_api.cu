@@ -291,6 +291,10 @@ int dcn_debug_tc_points(const dcn_problem* p, const void* offset, int32_t n, voi
                                 ws_bytes, static_cast<cudaStream_t>(stream));
 }
 
+int dcn_debug_expire_wait(int32_t* gave_up, void* stream) {
+    return dcn::tc_debug_expire_wait(gave_up, static_cast<cudaStream_t>(stream));
+}
+
 int dcn_check_status(void* stream) { return dcn::tc_check_status(static_cast<cudaStream_t>(stream)); }
 
 // ------------------------------------------------------------------------------------------------

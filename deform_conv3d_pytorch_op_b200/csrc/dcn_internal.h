@@ -37,6 +37,7 @@ int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const
                       const float* bias, float* y, cudaStream_t st);
 size_t tc_static_scratch_bytes();
 int tc_check_status(cudaStream_t st);
+int tc_debug_expire_wait(int* gave_up, cudaStream_t st);
 int tc_launch_count(const Geom& g, int ndim, int deform, int pass);
 int tc_debug_points(const Geom& g, int ndim, int deform, const float* off, int n, float* coords, int32_t* valid,
                     int32_t* lo, int32_t* hi, void* ws, size_t ws_bytes, cudaStream_t st);

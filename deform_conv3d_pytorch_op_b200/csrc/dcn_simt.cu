@@ -509,7 +509,10 @@ int launch_backward_weight(const Geom& g, const void* x, const void* off, const 
     const long long chunks = (g.P + 15) / 16;
     const long long tiles = (long long)((g.Kg + 63) / 64) * g.G * ((g.Og + 63) / 64);
     // aim for ~8 CTAs per SM overall, at least 8 chunks per split
-    long long splits = (148 * 8 + tiles - 1) / tiles;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms < 1) sms = 148;
+    long long splits = ((long long)sms * 8 + tiles - 1) / tiles;
     if (splits > chunks / 8) splits = chunks / 8;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;

@@ -497,6 +497,26 @@ int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const
     return tc_forward(g, ndim, deform, x, off, w, bias, y, ptr, kStaticScratchBytes, st);
 }
 
+// A wait that cannot complete: one thread waits, with a limit of about a millisecond, on a barrier nothing ever
+// arrives on.  It must give up, raise the status word and return -- the path every pipeline role of the kernels
+// above takes when its bounded wait runs out.  For the test of that path only.
+namespace {
+__global__ void expire_wait_kernel(long long limit_cycles, int* gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+        const bool ok = mbar_wait(&bar, 0, limit_cycles);
+        if (gave_up != nullptr) *gave_up = ok ? 0 : 1;
+    }
+}
+}  // namespace
+
+int tc_debug_expire_wait(int* gave_up, cudaStream_t st) {
+    expire_wait_kernel<<<1, 32, 0, st>>>(2000000ll, gave_up);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 int tc_check_status(cudaStream_t st) {
     if (cudaStreamSynchronize(st) != cudaSuccess) return -5;
     unsigned int v = 0;

@@ -66,12 +66,12 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
         : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and raises the status word) when the limit is reached.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: returns false (and raises the status word) when the limit (in clock cycles) is reached.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait_hint(bar, parity, kWaitParkNs)) {
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > limit) {
             atomicOr(&g_tc_status, 1u);
             return false;
         }

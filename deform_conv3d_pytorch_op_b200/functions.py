@@ -17,7 +17,7 @@ import torch
 from torch.autograd import Function
 from torch.autograd.function import once_differentiable
 
-from .ops import Op
+from .ops import Op, check_status, status_check_enabled
 
 
 def _tup(v, n):
@@ -52,7 +52,10 @@ class _ConvOffsetNdFunction(Function):
         want_db = ctx.has_bias and need[3]
         xcl = ctx.fwd_ws if (ctx.fwd_ws is not None and inputs._version == ctx.x_version) else None
         ctx.fwd_ws = None
-        return ctx.op.backward(inputs, offset, weight, grad_output, need[0], need[1], need[2], want_db, xcl)
+        grads = ctx.op.backward(inputs, offset, weight, grad_output, need[0], need[1], need[2], want_db, xcl)
+        if status_check_enabled() and not torch.cuda.is_current_stream_capturing():
+            check_status(inputs.device)
+        return grads
 
 
 class ConvOffset3dFunction(_ConvOffsetNdFunction):

@@ -29,6 +29,22 @@ def default_oob_offset_grad() -> bool:
     return os.environ.get("DCN_OOB_OFFSET_GRAD", "reference").lower() != "zero"
 
 
+def check_status(device=None) -> None:
+    """Reads and clears the library's device-side status word on ``device`` (default: the current CUDA device)
+    and raises :class:`DcnError` if a bounded device-side wait of a tensor-core kernel gave up since the last
+    check.  Synchronises the device's current stream.  The word is sticky and process-wide per device, so a check
+    tells that *some* call since the previous check failed, not which one: check once per step (or per call while
+    debugging; ``DCN_CHECK_STATUS=1`` makes every backward pass of the autograd Functions do so)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().dcn_check_status(_lib.current_stream(dev)), "device status")
+
+
+def status_check_enabled() -> bool:
+    """``DCN_CHECK_STATUS=1``: poll the status word after every backward pass (never inside a stream capture)."""
+    return os.environ.get("DCN_CHECK_STATUS", "0") not in ("", "0")
+
+
 def _prep(t: Optional[torch.Tensor], name: str, ref: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     if t is None:
         return None

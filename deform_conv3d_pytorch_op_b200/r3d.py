@@ -124,14 +124,19 @@ def all_reduce_grads(model: nn.Module, world: int, bucket_bytes: int = 25 << 20)
 
 
 def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor, labels: torch.Tensor,
-               world: int = 1, ddp: bool = False) -> torch.Tensor:
-    """forward + cross-entropy + backward + gradient all-reduce + SGD step on this rank's shard."""
+               world: int = 1, ddp: bool = False, check_status: bool = False) -> torch.Tensor:
+    """forward + cross-entropy + backward + gradient all-reduce + SGD step on this rank's shard.
+    ``check_status``: read the library's device status word after the step (synchronises the stream; raises if a
+    bounded device-side wait gave up) -- meant for every N-th step of a training loop."""
     opt.zero_grad(set_to_none=True)
     loss = F.cross_entropy(model(clips), labels)
     loss.backward()
     if world > 1 and not ddp:
         all_reduce_grads(model.module if hasattr(model, "module") else model, world)
     opt.step()
+    if check_status:
+        from .ops import check_status as _check
+        _check(clips.device)
     return loss.detach()
 
 
@@ -164,7 +169,8 @@ class GraphedTrainStep:
         loss.backward()
         return loss.detach()
 
-    def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None,
+                 check_status: bool = False) -> torch.Tensor:
         if clips is not None:
             self.clips.copy_(clips, non_blocking=True)      # keeps the static buffer's memory format
         if labels is not None:
@@ -173,4 +179,7 @@ class GraphedTrainStep:
         if self.world > 1:
             all_reduce_grads(self.model, self.world)
         self.opt.step()
+        if check_status:                                    # after the replay, outside any capture
+            from .ops import check_status as _check
+            _check(self.clips.device)
         return self.loss

@@ -122,7 +122,11 @@ int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const v
  * may load the library's device code), so make that first call outside any stream capture.  All calls on a
  * device share the one array, which keeps the previous call's contents; this pass overwrites every byte it
  * later reads, so nothing needs clearing, but two calls whose kernels overlap on the GPU (different
- * streams, or different host threads) race on it: serialise them. */
+ * streams, or different host threads) race on it: serialise them.  The resolved address is cached per device
+ * ordinal for the life of the process and does not survive cudaDeviceReset or the destruction of the device's
+ * primary context.  With CUDA's lazy module loading the first launch of each kernel variant (2-D / 3-D,
+ * deformable / plain, reference / channels-last layout) may load device code as well: call once per kind of
+ * problem before any stream capture. */
 size_t dcn_static_scratch_bytes(void);
 int dcn_forward_static_scratch(const dcn_problem* p, const void* x, const void* offset, const void* weight,
                                const void* bias, void* y, void* stream);
@@ -167,6 +171,12 @@ int dcn_debug_points(const dcn_problem* p, const void* offset, int32_t n, void* 
  * (3-D, more than 16 taps, planes too large for shared memory).  fp32 tensors, precision BF16. */
 int dcn_debug_tc_points(const dcn_problem* p, const void* offset, int32_t n, void* coords, int32_t* valid,
                         int32_t* lo, int32_t* hi, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Test aid for the error path of the bounded device-side waits: launches one thread that waits, with a limit of
+ * about a millisecond, on a barrier nothing arrives on.  The wait gives up, the kernel returns normally (nothing
+ * traps, the context stays usable), *gave_up (device pointer, may be NULL) is set to 1 and the next
+ * dcn_check_status reports DCN_ERR_TIMEOUT.  No counterpart in the reference (its kernels have no error path). */
+int dcn_debug_expire_wait(int32_t* gave_up, void* stream);
 
 /* Reads and clears the sticky device-side status word of the tensor-core kernels (bounded waits that
  * gave up).  Synchronises `stream`.  DCN_OK or DCN_ERR_TIMEOUT. */

@@ -188,3 +188,25 @@ def test_fixed_point_plane_budget_and_early_spill():
     assert dx_ref[0, 0, 5, 9] == H * W * 9 * O          # all 5184 samples of a channel land on one pixel
     assert cases.rel_err(dx.cpu().numpy(), dx_ref) <= 1e-5
     assert cases.rel_err(dx_s.cpu().numpy(), dx_ref) <= 1e-5
+
+
+def test_bounded_wait_gives_up_and_reports_timeout():
+    """A device-side wait that cannot complete (a barrier nothing arrives on) runs into its limit: the kernel
+    returns, the status word reports DCN_ERR_TIMEOUT once, and the library keeps working afterwards."""
+    from deform_conv3d_pytorch_op_b200 import _lib
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    st = _lib.current_stream(dev)
+    assert L.dcn_check_status(st) == 0
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert L.dcn_debug_expire_wait(_lib.ptr(flag), st) == 0
+    assert L.dcn_check_status(st) == -6                  # DCN_ERR_TIMEOUT
+    assert int(flag.item()) == 1
+    assert L.dcn_check_status(st) == 0                   # reading clears the word
+    with pytest.raises(_lib.DcnError):
+        assert L.dcn_debug_expire_wait(None, st) == 0
+        _lib.check(L.dcn_check_status(st), "device status")
+    case = cases.TC_CASES[0]
+    ours = helpers.run_ours(case, cases.make_inputs(case), "bf16")      # the context is still usable
+    _check_status()
+    assert np.isfinite(ours["y"]).all()

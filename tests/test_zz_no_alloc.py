@@ -46,6 +46,7 @@ def test_static_scratch_forward_matches_workspace_forward(name):
     dev = torch.device("cuda")
     stream = _lib.current_stream(dev)
     prob = _problem(case)
+    free_before_second_call = None
     for seed in (0, 1):                                    # two calls in a row on the shared array
         x, w, off, dy, b = [None if t is None else t.to(dev) for t in cases.make_inputs(case, seed=seed)]
         out_shape = (case.N, case.O) + _lib.output_size(prob)
@@ -55,9 +56,15 @@ def test_static_scratch_forward_matches_workspace_forward(name):
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         _lib.check(L.dcn_forward(ctypes.byref(prob), _lib.ptr(x), _lib.ptr(off), _lib.ptr(w), _lib.ptr(b),
                                  _lib.ptr(y_ws), _lib.ptr(ws), nbytes, stream), "dcn_forward")
+        if seed == 1:
+            torch.cuda.synchronize()
+            free_before_second_call = torch.cuda.mem_get_info(dev)[0]
         _lib.check(L.dcn_forward_static_scratch(ctypes.byref(prob), _lib.ptr(x), _lib.ptr(off), _lib.ptr(w),
                                                 _lib.ptr(b), _lib.ptr(y_st), stream), "dcn_forward_static_scratch")
         torch.cuda.synchronize()
+        if seed == 1:
+            # nothing was allocated on the device by the call (the first call may have loaded device code)
+            assert torch.cuda.mem_get_info(dev)[0] == free_before_second_call
         _lib.check(L.dcn_check_status(stream), "device status")
         a, r = y_st.cpu().numpy(), y_ws.cpu().numpy()
         assert np.isfinite(a).all() and np.isfinite(r).all()
@@ -89,3 +96,25 @@ def test_static_scratch_forward_takes_channels_last_activations():
     a, r = y_cl.permute(0, 3, 1, 2).cpu().numpy(), y_ref.cpu().numpy()
     assert np.isfinite(a).all()
     assert cases.rel_err(a, r) <= 1e-5, cases.rel_err(a, r)
+
+
+@pytest.mark.gpu
+def test_static_scratch_address_is_resolved_per_device():
+    """On a box with several GPUs the fixed array's address is resolved for each device separately."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU")
+    from deform_conv3d_pytorch_op_b200 import _lib
+    L = _lib.lib()
+    case = {c.name: c for c in cases.TC_CASES}["tc2_small"]
+    prob = _problem(case)
+    outs = []
+    for d in (0, 1):
+        dev = torch.device("cuda", d)
+        with torch.cuda.device(dev):
+            x, w, off, dy, b = [None if t is None else t.to(dev) for t in cases.make_inputs(case)]
+            y = torch.full((case.N, case.O) + _lib.output_size(prob), float("nan"), device=dev)
+            _lib.check(L.dcn_forward_static_scratch(ctypes.byref(prob), _lib.ptr(x), _lib.ptr(off), _lib.ptr(w),
+                                                    _lib.ptr(b), _lib.ptr(y), _lib.current_stream(dev)), "device %d" % d)
+            torch.cuda.synchronize(dev)
+            outs.append(y.cpu().numpy())
+    assert np.isfinite(outs[0]).all() and np.array_equal(outs[0], outs[1])
