@@ -76,34 +76,72 @@ to_channels_last_bf16(const float* __restrict__ x, __nv_bfloat16* __restrict__ x
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Pre-pass 2: weight [O, Cg, kv] fp32 -> swizzled K-major bf16 tiles [G][MT][KC][128 rows x 64 k],
-// GEMM-K index k' = tap * Cg + c.  Rows >= Og and k' >= kv*Cg are zero.
+// Pre-pass 2: weights.  Step one reorders and rounds the weight once, with coalesced reads and writes:
+//   W [O][Cg][kv] fp32  ->  Wt [O][kv * Cg] bf16,  GEMM-K order k' = tap * Cg + c
+// (a block takes one output channel and walks its row in pieces of 64 input channels through shared memory;
+// reading W directly in k' order would be a stride-kv gather, 8 to 27 times the traffic).  It also raises
+// *wmax_bits to the bit pattern of max|W| when asked to.  The operand tiles of the three passes are then cut out
+// of Wt, every tile row being a contiguous run of it.
 // ---------------------------------------------------------------------------------------------------
+constexpr int kWtChunk = 64;       // input channels per shared-memory piece
+
 __global__ void __launch_bounds__(256)
-pack_weight_fwd(const Geom g, const float* __restrict__ w, uint8_t* __restrict__ wpk, int MT, int KC) {
+weight_to_kmajor_bf16(const Geom g, const float* __restrict__ w, __nv_bfloat16* __restrict__ wt,
+                      unsigned int* __restrict__ wmax_bits) {
+    extern __shared__ float wrow[];                                  // [<= 64 channels][kv]
+    const int o = blockIdx.x;
+    const float* src = w + (size_t)o * g.Cg * g.kv;
+    __nv_bfloat16* dst = wt + (size_t)o * g.Kg;
+    float mx = 0.f;
+    for (int c0 = 0; c0 < g.Cg; c0 += kWtChunk) {
+        const int nc = g.Cg - c0 < kWtChunk ? g.Cg - c0 : kWtChunk;
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * g.kv; i += blockDim.x) {
+            const float v = __ldg(src + (size_t)c0 * g.kv + i);
+            wrow[i] = v;
+            mx = fmaxf(mx, fabsf(v));
+        }
+        __syncthreads();
+        // pairs of channels of one tap: consecutive threads write consecutive 4-byte words of a tap's row segment
+        const int np = nc / 2;                                       // channel counts are multiples of 8
+        for (int i = threadIdx.x; i < np * g.kv; i += blockDim.x) {
+            const int tap = i / np, cp = i - tap * np;
+            const uint32_t v = pack_bf16x2(wrow[(2 * cp) * g.kv + tap], wrow[(2 * cp + 1) * g.kv + tap]);
+            *reinterpret_cast<uint32_t*>(dst + (size_t)tap * g.Cg + c0 + 2 * cp) = v;
+        }
+    }
+    if (wmax_bits != nullptr) {
+        const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(mx));
+        if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(wmax_bits, m);
+    }
+}
+
+size_t wt_bytes(const Geom& g) { return align_up((size_t)g.O * g.Kg * 2, 256); }
+
+int launch_weight_to_kmajor(const Geom& g, const float* w, __nv_bfloat16* wt, unsigned int* wmax_bits, cudaStream_t st) {
+    const int smem = kWtChunk * g.kv * (int)sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(weight_to_kmajor_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -5;
+    weight_to_kmajor_bf16<<<g.O, 256, smem, st>>>(g, w, wt, wmax_bits);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Wt -> swizzled K-major bf16 tiles [G][MT][KC][128 rows x 64 k'] of the forward pass.  Rows >= Og and
+// k' >= kv*Cg are zero.  One thread per 16-byte chunk (8 consecutive k').
+__global__ void __launch_bounds__(256)
+pack_weight_fwd(const Geom g, const __nv_bfloat16* __restrict__ wt, uint8_t* __restrict__ wpk, int MT, int KC) {
     const int tile = blockIdx.x;                  // (j * MT + mt) * KC + kc
     const int kc = tile % KC, mt = (tile / KC) % MT, j = tile / KC / MT;
     uint8_t* dst = wpk + (size_t)tile * kTileBytes;
     for (int e = threadIdx.x; e < 128 * 8; e += blockDim.x) {
         const int row = e / 8, chunk = e % 8;
         const int o = mt * 128 + row;
-        uint32_t pk[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float v[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int kp = kc * kTileK + chunk * 8 + q * 2 + h;
-                float val = 0.f;
-                if (o < g.Og && kp < g.kv * g.Cg) {
-                    const int tap = kp / g.Cg, cl = kp % g.Cg;
-                    val = w[((size_t)(j * g.Og + o) * g.Cg + cl) * g.kv + tap];
-                }
-                v[h] = val;
-            }
-            pk[q] = pack_bf16x2(v[0], v[1]);
-        }
-        *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        const int kp = kc * kTileK + chunk * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (o < g.Og && kp < g.Kg)                // Kg is a multiple of 8: a chunk is inside or outside as a whole
+            v = __ldg(reinterpret_cast<const uint4*>(wt + (size_t)(j * g.Og + o) * g.Kg + kp));
+        *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) = v;
     }
 }
 
@@ -159,7 +197,7 @@ int sm_count() {
 #include "dcn_tc_fwd.cuh"
 
 struct FwdWorkspace {
-    size_t xcl_off, xcl_bytes, wpk_off, wpk_bytes, total;
+    size_t xcl_off, xcl_bytes, wpk_off, wpk_bytes, wt_off, total;
 };
 FwdWorkspace fwd_workspace(const Geom& g) {
     const TcDims d = tc_dims(g);
@@ -168,7 +206,8 @@ FwdWorkspace fwd_workspace(const Geom& g) {
     w.xcl_bytes = align_up((size_t)g.N * g.iv * g.C * 2, 256);
     w.wpk_off = w.xcl_bytes;
     w.wpk_bytes = align_up((size_t)g.G * d.MT * d.KC * kTileBytes, 256);
-    w.total = w.wpk_off + w.wpk_bytes;
+    w.wt_off = w.wpk_off + w.wpk_bytes;
+    w.total = w.wt_off + wt_bytes(g);
     return w;
 }
 
@@ -217,7 +256,7 @@ BwdWeightWorkspace bwd_weight_workspace(const Geom& g) {
 }
 
 struct BwdDataWorkspace {
-    size_t xcl_off, dpk_off, wpk_off, scale_off, dxcl_off, dxcl_bytes, dwpk_off, total;   // dwpk: fused backward only
+    size_t xcl_off, dpk_off, wpk_off, scale_off, wt_off, dxcl_off, dxcl_bytes, dwpk_off, total;   // dwpk: fused backward only
 };
 BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     const DgDims d = dg_dims(g);
@@ -228,7 +267,8 @@ BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     size_t wpk_bytes = (size_t)g.G * d.NB * d.OC * 2 * kTileBytes;
     if (g.Cg % 8 == 0 && b2_wpk_bytes(g) > wpk_bytes) wpk_bytes = b2_wpk_bytes(g);   // slab-wise tiles of dcn_tc_bwd2d.cuh
     w.scale_off = w.wpk_off + align_up(wpk_bytes, 256);
-    w.dxcl_off = w.scale_off + 256;                    // two words: bit patterns of max|dy| and max|W|
+    w.wt_off = w.scale_off + 256;                      // two words: bit patterns of max|dy| and max|W|
+    w.dxcl_off = w.wt_off + wt_bytes(g);
     w.dxcl_bytes = align_up((size_t)g.N * g.iv * g.C * 4, 256);
     // the shared-memory-accumulating kernel has no channels-last dX scratch; its sampling-point entries live there
     if (g.Cg % 8 == 0 && b2_points_bytes(g) > w.dxcl_bytes) w.dxcl_bytes = align_up(b2_points_bytes(g), 256);
@@ -246,7 +286,8 @@ bool use_bwd2d(const Geom& g, int ndim, int deform) {
 
 // dy packed (max|dy| taken on the way), slab-wise weight tiles (max|W|), cleared dOffset, then the kernel.
 int run_bwd2d(const Geom& g, const __nv_bfloat16* xcl, const float* off, const float* w, const float* dy, uint8_t* dpk,
-              uint8_t* wpk, unsigned int* scale, uint4* pts, float* dx, float* doff, bool accumulate, cudaStream_t st) {
+              uint8_t* wpk, __nv_bfloat16* wt, unsigned int* scale, uint4* pts, float* dx, float* doff, bool accumulate,
+              cudaStream_t st) {
     const B2Dims d = b2_dims(g);
     {
         const long long total = (long long)g.N * g.dg * g.kv * g.ov;
@@ -258,7 +299,9 @@ int run_bwd2d(const Geom& g, const __nv_bfloat16* xcl, const float* off, const f
     if (cudaMemsetAsync(scale, 0, 8, st) != cudaSuccess) return -5;
     int r = launch_pack_dy(g, dy, dpk, d.MT, d.PC, st, scale);
     if (r != 0) return r;
-    pack_weight_slab<<<g.G * d.SL * d.OC, 256, 0, st>>>(g, w, wpk, d.SL, d.OC, scale + 1);
+    r = launch_weight_to_kmajor(g, w, wt, scale + 1, st);
+    if (r != 0) return r;
+    pack_weight_slab<<<g.G * d.SL * d.OC, 256, 0, st>>>(g, wt, wpk, d.SL, d.OC);
     if (cudaGetLastError() != cudaSuccess) return -5;
     if (doff != nullptr &&
         cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * 2 * g.ov * sizeof(float), st) != cudaSuccess)
@@ -286,15 +329,15 @@ size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
 // Kernels a pass enqueues when every gradient is wanted (memsets not counted).
 int tc_launch_count(const Geom& g, int ndim, int deform, int pass) {
     const bool b2 = use_bwd2d(g, ndim, deform);
-    if (pass == 0) return 3;      // channels-last copy, weight pack, implicit GEMM
+    if (pass == 0) return 4;      // channels-last copy, weight reorder, weight tiles, implicit GEMM
     if (pass == 1) {
-        if (b2) return 5;         // input copy, sampling points, dy pack, slab weight pack, GEMM + shared-memory scatter
-        return g.cl ? 4 : 5;      // input copy, dy pack, weight pack, implicit GEMM + scatter, (dx transpose-add)
+        if (b2) return 6;         // input copy, sampling points, dy pack, weight reorder, slab tiles, GEMM + scatter
+        return g.cl ? 5 : 6;      // input copy, dy pack, weight reorder, weight tiles, GEMM + scatter, (dx transpose-add)
     }
     if (pass == 2) return 4;      // channels-last copy, dy pack, implicit GEMM, dW unpack
     // fused backward (input copy taken over from the forward pass when the caller hands it in: counted here)
-    if (b2) return 7;             // input copy, sampling points, dy pack, slab weight pack, dgrad, wgrad, dW unpack
-    return g.cl ? 6 : 7;          // input copy, dy pack, weight pack, dgrad, (dx transpose,) wgrad, dW unpack
+    if (b2) return 8;             // input copy, points, dy pack, weight reorder, slab tiles, dgrad, wgrad, dW unpack
+    return g.cl ? 7 : 8;          // input copy, dy pack, weight reorder, weight tiles, dgrad, (dx transpose,) wgrad, dW unpack
 }
 
 int tc_debug_points(const Geom& g, int ndim, int deform, const float* off, int n, float* coords, int32_t* valid,
@@ -323,7 +366,10 @@ int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float*
     const TcDims d = tc_dims(g);
     int r = launch_channels_last(g, x, xcl, st);
     if (r != 0) return r;
-    pack_weight_fwd<<<g.G * d.MT * d.KC, 256, 0, st>>>(g, w, wpk, d.MT, d.KC);
+    __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(base + l.wt_off);
+    r = launch_weight_to_kmajor(g, w, wt, nullptr, st);
+    if (r != 0) return r;
+    pack_weight_fwd<<<g.G * d.MT * d.KC, 256, 0, st>>>(g, wt, wpk, d.MT, d.KC);
     if (cudaGetLastError() != cudaSuccess) return -5;
     if (ndim == 2) return deform ? launch_tc_forward<2, true>(g, xcl, off, wpk, bias, y, st)
                                  : launch_tc_forward<2, false>(g, xcl, off, wpk, bias, y, st);
@@ -350,11 +396,15 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
         if (r != 0) return r;
     }
     if (use_bwd2d(g, ndim, deform))
-        return run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<unsigned int*>(base + l.scale_off),
+        return run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off),
+                         reinterpret_cast<unsigned int*>(base + l.scale_off),
                          reinterpret_cast<uint4*>(base + l.dxcl_off), dx, doff, true, st);
     r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
     if (r != 0) return r;
-    pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
+    r = launch_weight_to_kmajor(g, w, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off), nullptr, st);
+    if (r != 0) return r;
+    pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, reinterpret_cast<const __nv_bfloat16*>(base + l.wt_off), wpk,
+                                                       d.NB, d.OC);
     if (cudaGetLastError() != cudaSuccess) return -5;
     if (dxcl != nullptr && !g.cl && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
     if (doff != nullptr &&
@@ -427,7 +477,8 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
     }
     const bool b2 = (dx != nullptr || doff != nullptr) && use_bwd2d(g, ndim, deform);
     if (b2) {
-        r = run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<unsigned int*>(base + l.scale_off),
+        r = run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off),
+                      reinterpret_cast<unsigned int*>(base + l.scale_off),
                       reinterpret_cast<uint4*>(base + l.dxcl_off), dx, doff, false, st);
         if (r != 0) return r;
     } else {
@@ -435,7 +486,10 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         if (r != 0) return r;
     }
     if (!b2 && (dx != nullptr || doff != nullptr)) {
-        pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, w, wpk, d.NB, d.OC);
+        r = launch_weight_to_kmajor(g, w, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off), nullptr, st);
+        if (r != 0) return r;
+        pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, reinterpret_cast<const __nv_bfloat16*>(base + l.wt_off), wpk,
+                                                           d.NB, d.OC);
         if (cudaGetLastError() != cudaSuccess) return -5;
         if (dxcl != nullptr && cudaMemsetAsync(dxcl, 0, (size_t)g.N * g.iv * g.C * 4, st) != cudaSuccess) return -5;
         if (doff != nullptr &&

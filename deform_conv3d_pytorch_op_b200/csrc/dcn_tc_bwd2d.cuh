@@ -92,35 +92,32 @@ size_t b2_wpk_bytes(const Geom& g) {
     return (size_t)g.G * d.SL * d.w_bytes + 2048;     // + the rows an MMA reads past the last tile
 }
 
-// weight [O, Cg, kv] fp32 -> per (group, slab, 64-channel chunk of o) one K-major bf16 tile [kv * 8 rows][64 o],
-// row = tap * 8 + (channel within the slab), swizzled; o >= Og is zero.  Also raises *wmax_bits to the bit
-// pattern of max|W| (non-negative floats order like their bit patterns).
+// Wt [O][kv * Cg] bf16 (k' order) -> per (group, slab, 64-channel chunk of o) one K-major bf16 tile
+// [kv * 8 rows][64 o], row = tap * 8 + (channel within the slab), swizzled; o >= Og is zero.  The 8 channels of a
+// (slab, tap) are 16 contiguous bytes of Wt.
 __global__ void __launch_bounds__(256)
-pack_weight_slab(const Geom g, const float* __restrict__ w, uint8_t* __restrict__ wpk, int SL, int OC,
-                 unsigned int* __restrict__ wmax_bits) {
+pack_weight_slab(const Geom g, const __nv_bfloat16* __restrict__ wt, uint8_t* __restrict__ wpk, int SL, int OC) {
+    __shared__ __align__(16) uint16_t piece[64][16 * 8 + 8];        // [o][tap * 8 + c], up to 16 taps
     const int tile = blockIdx.x;                          // (j * SL + slab) * OC + oc
     const int oc = tile % OC, slab = (tile / OC) % SL, j = tile / OC / SL;
     uint8_t* dst = wpk + (size_t)tile * g.kv * 1024;
-    float mx = 0.f;
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(wt);
+    for (int e = threadIdx.x; e < 64 * g.kv; e += blockDim.x) {
+        const int ol = e / g.kv, tap = e - ol * g.kv;
+        const int o = oc * 64 + ol;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (o < g.Og) v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(j * g.Og + o) * g.Kg + (size_t)tap * g.Cg + slab * 8));
+        *reinterpret_cast<uint4*>(&piece[ol][tap * 8]) = v;
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < g.kv * 64; e += blockDim.x) {
-        const int row = e / 8, chunk = e % 8;
-        const int tap = row / 8, cl = row % 8;
+        const int row = e % (g.kv * 8), chunk = e / (g.kv * 8);
         uint32_t pk[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float v[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int ol = oc * 64 + chunk * 8 + q * 2 + h;
-                v[h] = ol < g.Og ? w[((size_t)(j * g.Og + ol) * g.Cg + slab * 8 + cl) * g.kv + tap] : 0.f;
-                mx = fmaxf(mx, fabsf(v[h]));
-            }
-            pk[q] = pack_bf16x2(v[0], v[1]);
-        }
+        for (int q = 0; q < 4; ++q)
+            pk[q] = (uint32_t)piece[chunk * 8 + 2 * q][row] | ((uint32_t)piece[chunk * 8 + 2 * q + 1][row] << 16);
         *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
-    const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(mx));
-    if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(wmax_bits, m);
 }
 
 // Sampling points, located once for all channel slabs of a deformable group.  One 16-byte entry per (sample,

@@ -27,29 +27,29 @@ struct DgSmem {
     static constexpr int kTotal = kBarOffset + (2 * kDgStages + 4) * 8 + 16;
 };
 
-// weight [O, Cg, kv] fp32 -> bf16 tiles [G][NB][OC][256 k' rows x 64 o], swizzled K-major.
+// Wt [O][kv * Cg] bf16 (k' order) -> bf16 tiles [G][NB][OC][256 k' rows x 64 o], swizzled K-major: the transpose of a
+// 64 x 256 piece of Wt through shared memory, 512-byte row reads and 128-byte tile-row writes.
 __global__ void __launch_bounds__(256)
-pack_weight_bwd(const Geom g, const float* __restrict__ w, uint8_t* __restrict__ wpk, int NB, int OC) {
+pack_weight_bwd(const Geom g, const __nv_bfloat16* __restrict__ wt, uint8_t* __restrict__ wpk, int NB, int OC) {
+    __shared__ __align__(16) uint16_t piece[64][256 + 8];   // [o][k'], rows padded against bank conflicts
     const int tile = blockIdx.x;                          // (j * NB + nb) * OC + oc
     const int oc = tile % OC, nb = (tile / OC) % NB, j = tile / OC / NB;
     uint8_t* dst = wpk + (size_t)tile * (2 * kTileBytes);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(wt);
+    for (int e = threadIdx.x; e < 64 * 32; e += blockDim.x) {
+        const int ol = e / 32, part = e % 32;
+        const int o = oc * 64 + ol, kq = nb * 256 + part * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (o < g.Og && kq < g.Kg) v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)(j * g.Og + o) * g.Kg + kq));
+        *reinterpret_cast<uint4*>(&piece[ol][part * 8]) = v;
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < 256 * 8; e += blockDim.x) {
-        const int row = e / 8, chunk = e % 8;
-        const int kq = nb * 256 + row;
+        const int row = e % 256, chunk = e / 256;         // consecutive threads read consecutive k' of one o
         uint32_t pk[4];
-        uint32_t tap = 0, cl = 0;
-        const bool kok = kq < g.kv * g.Cg;
-        if (kok) g.d_Cg.divmod((uint32_t)kq, tap, cl);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float v[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int ol = oc * 64 + chunk * 8 + q * 2 + h;
-                v[h] = (kok && ol < g.Og) ? w[((size_t)(j * g.Og + ol) * g.Cg + cl) * g.kv + tap] : 0.f;
-            }
-            pk[q] = pack_bf16x2(v[0], v[1]);
-        }
+        for (int q = 0; q < 4; ++q)
+            pk[q] = (uint32_t)piece[chunk * 8 + 2 * q][row] | ((uint32_t)piece[chunk * 8 + 2 * q + 1][row] << 16);
         *reinterpret_cast<uint4*>(dst + swz_offset(row, chunk)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
 }

@@ -72,3 +72,29 @@ def lattice_mask(case, off_np, tol=1e-6):
         near = np.repeat(near[:, :, None, :], nd, axis=2).reshape((-1,) + tuple(p.out_size))
         mask[n] = near
     return mask
+
+
+def offsets_at_fp32_coordinates(case, off_np):
+    """float64 offsets that make a float64 evaluation sample at exactly the coordinates the reference's fp32
+    arithmetic produces: p32 = fp32(base) + off32 (one fp32 rounding, deform3d/lib/deform_conv3d_cuda_kernel.cu:
+    117-119), returned as p32 - base in float64 (exact).  Validity (p > -1, p < size) and the truncation to corner
+    indices are discontinuous in p, so a float64 oracle fed the raw offsets disagrees with ANY fp32 implementation,
+    the reference included, at the few points whose fp32 coordinate rounds onto -1, size or an integer; with these
+    offsets the oracle takes the reference's decisions and does everything else in float64."""
+    p = case.problem()
+    nd = case.ndim
+    out_sz, k = tuple(p.out_size), tuple(p.kernel)
+    kv = int(np.prod(k))
+    N = off_np.shape[0]
+    dg = off_np.shape[1] // (kv * nd)
+    off32 = off_np.astype(np.float32).reshape((N, dg, kv, nd) + out_sz)
+    res = np.empty(off32.shape, dtype=np.float64)
+    taps = np.stack(np.unravel_index(np.arange(kv), k), axis=-1)             # [kv, nd]
+    for a in range(nd):
+        o = np.arange(out_sz[a], dtype=np.int64) * p.stride[a] - p.pad[a]     # [out_a]
+        shape_o = [1] * nd
+        shape_o[a] = out_sz[a]
+        base = o.reshape(shape_o)[None, None, None] + (taps[:, a] * p.dil[a]).reshape((1, 1, kv) + (1,) * nd)
+        p32 = base.astype(np.float32) + off32[:, :, :, a]
+        res[:, :, :, a] = p32.astype(np.float64) - base
+    return res.reshape(off_np.shape)

@@ -33,9 +33,9 @@ def test_channels_last_is_a_bf16_option(L):
     assert L.dcn_validate(ctypes.byref(_p(channels_last=True))) == -3            # exact precision: NCHW only
     ok = _p(C=16, O=16, G=1, cpg=16, precision=_lib.PREC_BF16, channels_last=True)
     assert L.dcn_validate(ctypes.byref(ok)) == 0
-    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 6        # no dx transpose pass
+    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 7        # no dx transpose pass
     ok.channels_last = 0
-    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 7
+    assert L.dcn_launch_count(ctypes.byref(ok), _lib.PASS_BACKWARD) == 8
     ok.channels_last = 2
     assert L.dcn_validate(ctypes.byref(ok)) == -3
 

@@ -33,9 +33,13 @@ def _status():
 
 
 def _oracle64(case, x, w, off, dy):
+    """The float64 oracle at the coordinates the reference's fp32 arithmetic produces (see
+    helpers.offsets_at_fp32_coordinates): among the 10^8 sampling points of a full-size configuration a few round
+    onto the validity boundary, where the operator is discontinuous."""
     p = case.problem()
     p.N = x.shape[0]
-    x64, o64, w64, dy64 = [t.numpy().astype(np.float64) for t in (x, off, w, dy)]
+    x64, w64, dy64 = [t.numpy().astype(np.float64) for t in (x, w, dy)]
+    o64 = helpers.offsets_at_fp32_coordinates(case, off.numpy())
     y = orc.forward(p, x64, o64, w64)
     dx, doff = orc.backward_data(p, x64, o64, w64, dy64)
     dw = orc.backward_weight(p, x64, o64, dy64)
