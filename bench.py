@@ -215,26 +215,15 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
-def run_model(args):
-    """Config 5: one SGD training step of the R3D-18-style network with deformable stages 3-4 on N = 64 clips of
-    3x16x112x112, the batch split over the ranks (strong scaling), parameter gradients all-reduced over NCCL."""
-    import torch.nn.functional as F
+def model_bench(args, world, rank, local, dev, steps, warm):
+    """Config 5: SGD training steps of the R3D-18-style network with deformable stages 3-4 on N = 64 clips of
+    3x16x112x112, the batch split over the ranks (strong scaling), parameter gradients all-reduced over NCCL in flat
+    buckets.  Returns the fields of the `model` object (rank 0; None elsewhere).  The process group is the
+    caller's."""
     from deform_conv3d_pytorch_op_b200 import r3d, _lib
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model and no CPU path; "
-                              "config 5 has no reference arm (operator-level arm: --config 1..4)"}), flush=True)
-        return
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU implementation)"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    total = args.batch if args.batch > 0 else 64
+    total = args.model_batch if args.model_batch > 0 else 64
     g = torch.Generator().manual_seed(0)
     labels_all = torch.randint(0, 400, (total,), generator=g)
     per = total // world
@@ -255,7 +244,7 @@ def run_model(args):
     net = model
     if use_ddp:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
-    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9, fused=True)
     x_d, y_d = x_h.to(dev), y_h.to(dev)
     if chl:
         x_d = x_d.contiguous(memory_format=torch.channels_last_3d)
@@ -266,13 +255,19 @@ def run_model(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    def rank_max(v):
+        if world > 1:
+            t = torch.tensor([v], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
     ev = lambda: torch.cuda.Event(enable_timing=True)
-    warm = max(args.warmup, 3)
     graphed = r3d.GraphedTrainStep(model, opt, x_d, y_d, world) if use_graph else None
 
-    def one_step(xd=None, yd=None):
+    def one_step(xd=None, yd=None, timed=False):
         if graphed is not None:
-            return graphed(xd, yd)
+            return graphed(xd, yd, timed=timed)
         return r3d.train_step(net, opt, x_d if xd is None else xd, y_d if yd is None else yd, world, ddp=use_ddp)
 
     for _ in range(warm):
@@ -284,16 +279,26 @@ def run_model(args):
     a, b = ev(), ev()
     sync_all()
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         one_step()
     b.record()
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
-    ms = a.elapsed_time(b) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = rank_max(a.elapsed_time(b) / steps)
+    # phases, in a separate short loop (the events between the phases do not serialise anything that was not
+    # already serial: replay, all-reduce and optimizer step are stream-ordered)
+    phases = None
+    if graphed is not None:
+        acc = [0.0, 0.0, 0.0]
+        n_ph = max(3, min(steps, 10))
+        for _ in range(n_ph):
+            one_step(timed=True)
+            torch.cuda.synchronize()
+            e = graphed.phase_events
+            for k in range(3):
+                acc[k] += e[k].elapsed_time(e[k + 1])
+        phases = {"compute_graph_replay": rank_max(acc[0] / n_ph), "grad_all_reduce": rank_max(acc[1] / n_ph),
+                  "optimizer": rank_max(acc[2] / n_ph)}
     _lib.check(_lib.lib().dcn_check_status(_lib.current_stream(dev)), "device status after the timed region")
 
     # end to end: the shard comes from pinned host memory every step and the loss goes back to the host
@@ -308,36 +313,63 @@ def run_model(args):
         for _ in range(2):
             e2e_step()
         sync_all()
-        n_e2e = max(3, min(args.steps, 10))
+        n_e2e = max(3, min(steps, 10))
         a.record()
         for _ in range(n_e2e):
             e2e_step()
         b.record()
         sync_all()
-        e_ms = a.elapsed_time(b) / n_e2e
-        if world > 1:
-            t = torch.tensor([e_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms = float(t.item())
+        e_ms = rank_max(a.elapsed_time(b) / n_e2e)
         e2e = {"value": total / (e_ms * 1e-3), "unit": "clips/s", "ms_per_step": e_ms,
                "h2d_bytes_per_step": (x_h.numel() * 4 + y_h.numel() * 8) * world, "d2h_bytes_per_step": 4 * world}
+    n_deform = sum(1 for m_ in model.modules() if isinstance(m_, r3d.DeformUnit))
+    n_param = sum(p.numel() for p in model.parameters())
+    del graphed, model, opt, net, x_d, y_d
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    return {"workload": "cfg5_r3d18_deform_stage3_4", "clips_per_s": total / (ms * 1e-3), "ms_per_step": ms,
+            "steps": steps, "warmup": warm, "global_batch": total, "per_gpu_batch": per, "n_gpus": world,
+            "scaling": "strong", "phases_ms": phases, "e2e": e2e, "clocks": clocks,
+            "clip": [3, 16, 112, 112], "classes": 400, "parameters": n_param, "optimizer": "SGD momentum 0.9, fused",
+            "parallelism": ("ddp x%d" % world) if use_ddp else ("flat-bucket all-reduce (mean) x%d" % world if world > 1 else "single GPU"),
+            "launch": "CUDA graph replay (forward + backward); all-reduce and optimizer eager" if use_graph else "eager",
+            "stock_layers": "channels_last_3d" if chl else "NCDHW", "deformable_layers": n_deform}
+
+
+def run_model(args):
+    """--config 5: the model-level workload alone, as its own JSON line."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference ships no model and no CPU path; "
+                              "config 5 has no reference arm (operator-level arm: --config 1..4)"}), flush=True)
+        return
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU implementation)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    args.model_batch = args.batch if args.batch > 0 else args.model_batch
+    warm = max(args.warmup, 3)
+    m = model_bench(args, world, rank, local, dev, args.steps, warm)
     if rank == 0:
-        n_deform = sum(1 for m_ in model.modules() if isinstance(m_, r3d.DeformUnit))
         line = {
-            "metric": "r3d18_deform_train_clips_per_s", "value": total / (ms * 1e-3), "unit": "clips/s",
-            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (deformable layers, fp32 I/O) + tf32/fp32 (cuDNN layers)",
-            "data": "synthetic",
-            "config": {"workload": "cfg5_r3d18_deform_stage3_4", "global_batch": total, "per_gpu_batch": per,
-                       "clip": [3, 16, 112, 112], "classes": 400, "optimizer": "SGD momentum 0.9",
-                       "parallelism": ("ddp x%d" % world) if use_ddp else ("bucketed all-reduce x%d" % world if world > 1 else "single GPU"),
-                       "launch": "CUDA graph replay" if use_graph else "eager",
-                       "stock_layers": "channels_last_3d" if chl else "NCDHW",
+            "metric": "r3d18_deform_train_clips_per_s", "value": m["clips_per_s"], "unit": "clips/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": m["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 (deformable layers, fp32 I/O) + tf32/fp32 (cuDNN layers)", "data": "synthetic",
+            "config": {"workload": m["workload"], "global_batch": m["global_batch"], "per_gpu_batch": m["per_gpu_batch"],
+                       "clip": m["clip"], "classes": 400, "optimizer": m["optimizer"], "parallelism": m["parallelism"],
+                       "launch": m["launch"], "stock_layers": m["stock_layers"],
                        "l2": "activations of one step exceed the 126 MB L2"},
-            "roofline": None, "cpu_baseline": None, "e2e": e2e, "clocks": clocks,
-            # 8 deformable layers x (3 forward + 7 fused backward) library launches per step (the other layers are
+            "roofline": None, "cpu_baseline": None, "e2e": m["e2e"], "clocks": m["clocks"], "model": m,
+            # per deformable layer and step: 4 forward + 8 fused backward library launches (the other layers are
             # cuDNN / torch)
-            "gpu_launches": n_deform * 10 * args.steps,
+            "gpu_launches": m["deformable_layers"] * 12 * args.steps,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -357,6 +389,9 @@ def main():
                     help="config 5: keep the stock layers in NCDHW instead of channels_last_3d")
     ap.add_argument("--precision", default="auto", choices=["auto", "exact", "bf16"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (0: the configuration's)")
+    ap.add_argument("--model-batch", type=int, default=64, help="global batch (clips) of the model-level workload")
+    ap.add_argument("--no-model", action="store_true",
+                    help="leave the model-level workload (config 5, the `model` object) out of the operator line")
     ap.add_argument("--ref-samples", type=int, default=0,
                     help="samples per step of the --impl reference arm (0: the whole per-GPU batch)")
     ap.add_argument("--cpu-baseline-samples", type=int, default=16)
@@ -557,6 +592,15 @@ def main():
         e2e = {"value": wl.flops() * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
+    # ---- the model-level workload (config 5) of the same metric, on the same ranks, as the `model` object ----
+    model_obj = None
+    if not args.no_model:
+        del x, off, dy, op
+        if flush_buf is not None:
+            flush_buf = None
+        torch.cuda.empty_cache()
+        model_obj = model_bench(args, world, rank, local, dev, max(3, min(args.steps, 10)), 3)
+
     if rank == 0:
         peaks = _peaks()
         dom = max(pass_ms, key=pass_ms.get)
@@ -605,7 +649,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
             "config": our_config(wl, prec, world, flush, working_set),
-            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "model": model_obj,
             "gpu_launches": launches_per_step * args.steps,
         }
         print(json.dumps(line), flush=True)

@@ -211,23 +211,6 @@ __device__ __forceinline__ int atom_shared_exch(uint32_t addr, int v) {
     return old;
 }
 
-// Bounded wait of the single-lane roles (MMA issue, loader): they have slack, so the lane sleeps between polls
-// instead of taking issue slots from the epilogue warps of its scheduler.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i) {                 // the clock is read once per 64 polls only
-            if (mbar_try_wait_hint(bar, parity, kWaitParkNs)) return true;
-        }
-        if (clock64() - t0 > kWaitCycles) {
-            atomicOr(&g_tc_status, 1u);
-            return false;
-        }
-    }
-}
-
 struct B2Item {
     int n, j, slab;
     int ch0;            // first input channel of the slab
@@ -304,13 +287,13 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
             const uint32_t w_base = smem_u32(wres);
             for (long long item = blockIdx.x; item < d.items && ok; item += gridDim.x, ++il) {
                 const B2Item wi = b2_item(g, item, d.SL);
-                ok = mbar_wait_relaxed(&ctl->w_full, il & 1);
+                ok = mbar_wait(&ctl->w_full, il & 1);
                 for (int t = 0; t < wi.tiles && ok; ++t, ++tl) {
                     const uint32_t b = tl & 1;
-                    ok = mbar_wait_relaxed(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
+                    ok = mbar_wait(&ctl->acc_empty[b], ((tl >> 1) & 1) ^ 1);
                     tc_fence_after();
                     for (int os = 0; os < d.OS && ok; ++os, rs.next(NS)) {
-                        ok = mbar_wait_relaxed(&ctl->full[rs.i], rs.ph);
+                        ok = mbar_wait(&ctl->full[rs.i], rs.ph);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t a_base = smem_u32(ring + rs.i * kB2StageBytes);
@@ -336,7 +319,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
             bool ok = true;
             for (long long item = blockIdx.x; item < d.items && ok; item += gridDim.x, ++il) {
                 const B2Item wi = b2_item(g, item, d.SL);
-                ok = mbar_wait_relaxed(&ctl->w_empty, (il & 1) ^ 1);
+                ok = mbar_wait(&ctl->w_empty, (il & 1) ^ 1);
                 if (!ok) break;
                 mbar_arrive_expect_tx(&ctl->w_full, (uint32_t)d.w_bytes);
                 for (int oc = 0; oc < d.OC; ++oc)
@@ -344,7 +327,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
                              (uint32_t)d.w_chunk, &ctl->w_full);
                 for (int t = 0; t < wi.tiles && ok; ++t) {
                     for (int os = 0; os < d.OS && ok; ++os, rs.next(NS)) {
-                        ok = mbar_wait_relaxed(&ctl->empty[rs.i], rs.ph ^ 1u);
+                        ok = mbar_wait(&ctl->empty[rs.i], rs.ph ^ 1u);
                         if (!ok) break;
                         mbar_arrive_expect_tx(&ctl->full[rs.i], (uint32_t)kB2StageBytes);
                         uint8_t* a_dst = ring + rs.i * kB2StageBytes;
@@ -483,7 +466,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
                     // ---- col values of the group out of tensor memory; the accumulator is released once the
                     // position's last values are in registers
                     if (tg == k3) {
-                        ok = mbar_wait_relaxed(&ctl->acc_full[b], (tl >> 1) & 1);
+                        ok = mbar_wait(&ctl->acc_full[b], (tl >> 1) & 1);
                         if (!ok) break;
                         tc_fence_after();
                     }

@@ -97,30 +97,68 @@ def shard(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return t[rank * per:(rank + 1) * per]
 
 
+class GradBuckets:
+    """Parameter gradients as views into a few preallocated flat buffers.  The exchange step is then one in-place
+    all-reduce (mean) per buffer: nothing is concatenated, divided or copied back.  Buckets are filled in reverse
+    parameter order, the order in which backward produces the gradients.  Only parameter gradients cross the
+    network: no activation is exchanged."""
+
+    def __init__(self, model: nn.Module, bucket_bytes: int = 25 << 20):
+        self.flats = []
+        params = [p for p in reversed(list(model.parameters())) if p.requires_grad]
+        i = 0
+        while i < len(params):
+            group, size = [], 0
+            while i < len(params) and (not group or size + params[i].numel() * params[i].element_size() <= bucket_bytes):
+                if group and (params[i].dtype != group[0].dtype or params[i].device != group[0].device):
+                    break
+                group.append(params[i])
+                size += params[i].numel() * params[i].element_size()
+                i += 1
+            flat = torch.zeros(sum(p.numel() for p in group), dtype=group[0].dtype, device=group[0].device)
+            off = 0
+            for p in group:
+                # the view has the parameter's own strides (channels-last weights keep their layout)
+                p.grad = torch.as_strided(flat, p.size(), p.stride(), off) if _dense(p) else flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+            self.flats.append(flat)
+
+    def zero(self):
+        for f in self.flats:
+            f.zero_()
+
+    def all_reduce(self, world: int) -> int:
+        """Mean over the ranks, in place; returns the number of collectives issued."""
+        import torch.distributed as dist
+        if world <= 1:
+            return 0
+        for f in self.flats:
+            if dist.get_backend() == "nccl":
+                dist.all_reduce(f, op=dist.ReduceOp.AVG)
+            else:                                     # gloo has no AVG
+                dist.all_reduce(f)
+                f.div_(world)
+        return len(self.flats)
+
+
+def _dense(p: torch.Tensor) -> bool:
+    """True if the parameter's elements occupy numel() consecutive storage slots in some dimension order."""
+    return p.is_contiguous() or p.is_contiguous(memory_format=torch.channels_last_3d if p.dim() == 5 else
+                                                torch.channels_last if p.dim() == 4 else torch.contiguous_format)
+
+
 def all_reduce_grads(model: nn.Module, world: int, bucket_bytes: int = 25 << 20) -> int:
-    """Sum-all-reduce every parameter gradient in flat buckets and divide by the world size (mean over the
-    global batch).  Only parameter gradients cross the network: no activation is exchanged.  Returns the number
-    of collectives issued."""
-    import torch.distributed as dist
-    grads = [p.grad for p in model.parameters() if p.grad is not None]
-    n_coll, i = 0, 0
-    while i < len(grads):
-        bucket, size = [], 0
-        while i < len(grads) and (not bucket or size + grads[i].numel() * grads[i].element_size() <= bucket_bytes):
-            if bucket and grads[i].dtype != bucket[0].dtype:
-                break
-            bucket.append(grads[i])
-            size += grads[i].numel() * grads[i].element_size()
-            i += 1
-        flat = torch.cat([g.reshape(-1) for g in bucket])
-        dist.all_reduce(flat)
-        flat.div_(world)
-        off = 0
-        for g in bucket:
-            g.copy_(flat[off:off + g.numel()].view_as(g))
-            off += g.numel()
-        n_coll += 1
-    return n_coll
+    """Mean-all-reduce of whatever gradients the parameters hold right now: they are moved into fresh flat buckets
+    (a training loop keeps one :class:`GradBuckets` instead and lets backward write into it, see
+    :func:`train_step`).  Returns the number of collectives issued."""
+    grads = {id(p): p.grad for p in model.parameters() if p.grad is not None}
+    gb = GradBuckets(model, bucket_bytes)
+    for p in model.parameters():
+        if id(p) in grads:
+            p.grad.copy_(grads[id(p)])
+        elif p.requires_grad:
+            p.grad.zero_()
+    return gb.all_reduce(world)
 
 
 def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor, labels: torch.Tensor,
@@ -128,11 +166,19 @@ def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor
     """forward + cross-entropy + backward + gradient all-reduce + SGD step on this rank's shard.
     ``check_status``: read the library's device status word after the step (synchronises the stream; raises if a
     bounded device-side wait gave up) -- meant for every N-th step of a training loop."""
-    opt.zero_grad(set_to_none=True)
+    inner = model.module if hasattr(model, "module") else model
+    gb = None
+    if world > 1 and not ddp:
+        gb = getattr(inner, "_grad_buckets", None)
+        if gb is None:
+            gb = inner._grad_buckets = GradBuckets(inner)
+        gb.zero()                                          # backward accumulates into the bucket views
+    else:
+        opt.zero_grad(set_to_none=True)
     loss = F.cross_entropy(model(clips), labels)
     loss.backward()
-    if world > 1 and not ddp:
-        all_reduce_grads(model.module if hasattr(model, "module") else model, world)
+    if gb is not None:
+        gb.all_reduce(world)
     opt.step()
     if check_status:
         from .ops import check_status as _check
@@ -143,15 +189,17 @@ def train_step(model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor
 class GraphedTrainStep:
     """Forward + backward of one training step captured in a CUDA graph and replayed: the network's few hundred
     small launches per step (late stages work on a handful of positions per clip) stop costing host time, which
-    is what bounds the step once the batch is split over several GPUs.  The gradient all-reduce (a few flat
-    buckets) and the optimizer step run eagerly after the replay, outside the capture.
-    Inputs are copied into static buffers before each replay."""
+    is what bounds the step once the batch is split over several GPUs.  Gradients live in flat buckets
+    (:class:`GradBuckets`); the all-reduce of the buckets and the optimizer step run eagerly after the replay,
+    outside the capture.  Inputs are copied into static buffers before each replay."""
 
     def __init__(self, model: nn.Module, opt: torch.optim.Optimizer, clips: torch.Tensor, labels: torch.Tensor,
                  world: int = 1, warmup: int = 3):
         self.model, self.opt, self.world = model, opt, world
         self.clips = clips.clone()
         self.labels = labels.clone()
+        self.buckets = GradBuckets(model)
+        model._grad_buckets = self.buckets
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -162,23 +210,35 @@ class GraphedTrainStep:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.loss = self._fwd_bwd()
+        self.phase_events = None
 
     def _fwd_bwd(self):
-        self.opt.zero_grad(set_to_none=False)
+        self.buckets.zero()                               # gradients accumulate into the bucket views
         loss = F.cross_entropy(self.model(self.clips), self.labels)
         loss.backward()
         return loss.detach()
 
     def __call__(self, clips: Optional[torch.Tensor] = None, labels: Optional[torch.Tensor] = None,
-                 check_status: bool = False) -> torch.Tensor:
+                 check_status: bool = False, timed: bool = False) -> torch.Tensor:
+        """``timed``: record CUDA events around the three phases (compute = graph replay, exchange = all-reduce,
+        optimizer) into ``self.phase_events`` (four events)."""
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if timed else None
         if clips is not None:
             self.clips.copy_(clips, non_blocking=True)      # keeps the static buffer's memory format
         if labels is not None:
             self.labels.copy_(labels, non_blocking=True)
+        if ev:
+            ev[0].record()
         self.graph.replay()
-        if self.world > 1:
-            all_reduce_grads(self.model, self.world)
+        if ev:
+            ev[1].record()
+        self.buckets.all_reduce(self.world)
+        if ev:
+            ev[2].record()
         self.opt.step()
+        if ev:
+            ev[3].record()
+            self.phase_events = ev
         if check_status:                                    # after the replay, outside any capture
             from .ops import check_status as _check
             _check(self.clips.device)

@@ -101,3 +101,53 @@ def test_deformable_network_trains_on_gpu():
             assert mod.offset.weight.grad is not None and float(mod.offset.weight.grad.abs().sum()) > 0
     from deform_conv3d_pytorch_op_b200 import _lib
     _lib.check(_lib.lib().dcn_check_status(_lib.current_stream(torch.device("cuda"))), "device status")
+
+
+def _make_deform(width=16, classes=10):
+    torch.manual_seed(0)
+    m = r3d.R3D18Deform(num_classes=classes, width=width, precision="exact", deform=True)
+    for mod in m.modules():
+        if isinstance(mod, torch.nn.BatchNorm3d):
+            mod.eval()
+        if isinstance(mod, r3d.DeformUnit):
+            torch.nn.init.normal_(mod.offset.weight, std=0.05)      # offsets that actually move the samples
+    return m
+
+
+def _gpu_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    m = _make_deform().to(dev)
+    x, y = _batch()
+    xs, ys = r3d.shard(x, rank, world).to(dev), r3d.shard(y, rank, world).to(dev)
+    gb = r3d.GradBuckets(m, bucket_bytes=1 << 18)          # backward writes straight into the flat buckets
+    torch.nn.functional.cross_entropy(m(xs), ys).backward()
+    n_coll = gb.all_reduce(world)
+    torch.cuda.synchronize()
+    if rank == 0:
+        torch.save({"grads": [p.grad.detach().cpu().clone() for p in m.parameters()], "n_coll": n_coll}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_with_deformable_layers_match_single_process(tmp_path):
+    """The real network (deformable stages 3-4, exact precision) on two GPUs, half a batch each, gradients averaged
+    through the flat buckets over NCCL, against one process on the whole batch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "g2.pt")
+    mp.spawn(_gpu_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out)
+    m = _make_deform().cuda()
+    x, y = _batch()
+    torch.nn.functional.cross_entropy(m(x.cuda()), y.cuda()).backward()
+    assert got["n_coll"] >= 2
+    for a, p in zip(got["grads"], m.parameters()):
+        ref = p.grad.cpu()
+        scale = max(float(ref.abs().max()), 1e-6)
+        assert float((a - ref).abs().max()) <= 2e-4 * scale + 1e-7, float((a - ref).abs().max()) / scale
