@@ -130,9 +130,10 @@ size_t dcn_workspace_bytes(const dcn_problem* p, int pass) {
 
 int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
-    if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_BACKWARD ? 2 : 1;
     Geom g;
     make_geom(p, g);
+    if (p->precision == DCN_PREC_EXACT)
+        return (pass == DCN_PASS_BACKWARD && !dcn::simt_backward_both_supported(g, p->dtype)) ? 2 : 1;
     if (!dcn::tc_supported(g, p->ndim, p->deformable)) return 0;
     return dcn::tc_launch_count(g, p->ndim, p->deformable, pass);
 }
@@ -252,11 +253,17 @@ int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const 
             if (dx != nullptr && cudaMemsetAsync(dx, 0, (size_t)g.N * g.C * g.iv * es, st) != cudaSuccess) return DCN_ERR_CUDA;
             if (dweight != nullptr && cudaMemsetAsync(dweight, 0, (size_t)g.O * g.Cg * g.kv * es, st) != cudaSuccess)
                 return DCN_ERR_CUDA;
-            if (dx != nullptr || doffset != nullptr)
-                r = dcn::simt_backward_data(g, p->dtype, p->ndim, p->deformable, x, offset, weight, dy, dx,
-                                            p->deformable ? doffset : nullptr, st);
-            if (r == DCN_OK && dweight != nullptr)
-                r = dcn::simt_backward_weight(g, p->dtype, p->ndim, p->deformable, x, offset, dy, dweight, st);
+            const bool all = dx != nullptr && dweight != nullptr && (!p->deformable || doffset != nullptr);
+            if (all && dcn::simt_backward_both_supported(g, p->dtype)) {
+                r = dcn::simt_backward_both(g, p->ndim, p->deformable, x, offset, weight, dy, dx,
+                                            p->deformable ? doffset : nullptr, dweight, st);     // one launch
+            } else {
+                if (dx != nullptr || doffset != nullptr)
+                    r = dcn::simt_backward_data(g, p->dtype, p->ndim, p->deformable, x, offset, weight, dy, dx,
+                                                p->deformable ? doffset : nullptr, st);
+                if (r == DCN_OK && dweight != nullptr)
+                    r = dcn::simt_backward_weight(g, p->dtype, p->ndim, p->deformable, x, offset, dy, dweight, st);
+            }
         }
         if (r != DCN_OK) return r;
     }

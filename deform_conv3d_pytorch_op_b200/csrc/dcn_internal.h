@@ -16,6 +16,9 @@ int simt_backward_data(const Geom& g, int dtype, int ndim, int deform, const voi
                        const void* w, const void* dy, void* dx, void* doff, cudaStream_t st);
 int simt_backward_weight(const Geom& g, int dtype, int ndim, int deform, const void* x, const void* off,
                          const void* dy, void* dw, cudaStream_t st);
+bool simt_backward_both_supported(const Geom& g, int dtype);
+int simt_backward_both(const Geom& g, int ndim, int deform, const void* x, const void* off, const void* w,
+                       const void* dy, void* dx, void* doff, void* dw, cudaStream_t st);
 int bias_grad(const Geom& g, int dtype, const void* dy, void* dbias, cudaStream_t st);
 int debug_points(const Geom& g, int dtype, int ndim, const void* off, int n, void* coords, int32_t* valid,
                  int32_t* lo, int32_t* hi, cudaStream_t st);

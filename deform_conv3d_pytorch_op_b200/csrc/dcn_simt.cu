@@ -141,8 +141,8 @@ simt_forward_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__
 // grid.x: tiles of BN positions; grid.y: G * ceil(Kg / BM)
 // ---------------------------------------------------------------------------------------------
 template <typename T, int D, bool DEFORM>
-__global__ void __launch_bounds__(kThreads)
-simt_backward_data_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off,
+__device__ __forceinline__ void
+simt_backward_data_body(const uint3 bid, const Geom g, const T* __restrict__ x, const T* __restrict__ off,
                           const T* __restrict__ w, const T* __restrict__ dy, T* __restrict__ dx,
                           T* __restrict__ doff) {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
@@ -157,9 +157,9 @@ simt_backward_data_kernel(const Geom g, const T* __restrict__ x, const T* __rest
 
     const int tid = threadIdx.x;
     const int mt_per_group = (g.Kg + BM - 1) / BM;
-    const int j = blockIdx.y / mt_per_group;
-    const int m0 = (blockIdx.y % mt_per_group) * BM;
-    const long long P0 = (long long)blockIdx.x * BN;
+    const int j = bid.y / mt_per_group;
+    const int m0 = (bid.y % mt_per_group) * BM;
+    const long long P0 = (long long)bid.x * BN;
     const int tx = tid % 16, ty = tid / 16;
 
     T acc[TM][TN];
@@ -340,13 +340,21 @@ simt_backward_data_kernel(const Geom g, const T* __restrict__ x, const T* __rest
     }
 }
 
+template <typename T, int D, bool DEFORM>
+__global__ void __launch_bounds__(kThreads)
+simt_backward_data_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off,
+                          const T* __restrict__ w, const T* __restrict__ dy, T* __restrict__ dx,
+                          T* __restrict__ doff) {
+    simt_backward_data_body<T, D, DEFORM>(blockIdx, g, x, off, w, dy, dx, doff);
+}
+
 // ---------------------------------------------------------------------------------------------
 // backward weight: dW[o, k] += sum_P dy[o, P] * sample(k, P);  grid.z splits the position range
 // grid.x: ceil(Kg / BN) ; grid.y: G * ceil(Og / BM)
 // ---------------------------------------------------------------------------------------------
 template <typename T, int D, bool DEFORM>
-__global__ void __launch_bounds__(kThreads)
-simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off,
+__device__ __forceinline__ void
+simt_backward_weight_body(const uint3 bid, const Geom g, const T* __restrict__ x, const T* __restrict__ off,
                             const T* __restrict__ dy, T* __restrict__ dw, int chunks_per_split) {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     __shared__ T As[BK][BM + 4];
@@ -354,9 +362,9 @@ simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __re
 
     const int tid = threadIdx.x;
     const int mt_per_group = (g.Og + BM - 1) / BM;
-    const int j = blockIdx.y / mt_per_group;
-    const int o0 = (blockIdx.y % mt_per_group) * BM;
-    const int k0 = blockIdx.x * BN;
+    const int j = bid.y / mt_per_group;
+    const int o0 = (bid.y % mt_per_group) * BM;
+    const int k0 = bid.x * BN;
     const int tx = tid % 16, ty = tid / 16;
 
     T acc[TM][TN];
@@ -366,7 +374,7 @@ simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __re
         for (int b = 0; b < TN; ++b) acc[a][b] = (T)0;
 
     const long long total_chunks = (g.P + BK - 1) / BK;
-    long long c_begin = (long long)blockIdx.z * chunks_per_split;
+    long long c_begin = (long long)bid.z * chunks_per_split;
     long long c_end = c_begin + chunks_per_split;
     if (c_end > total_chunks) c_end = total_chunks;
 
@@ -422,6 +430,33 @@ simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __re
 }
 
 // dbias[o] = sum over n and positions of dy  (deform3d/deform_conv3d_functions/deform_conv3d_function.py:73-74)
+template <typename T, int D, bool DEFORM>
+__global__ void __launch_bounds__(kThreads)
+simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off,
+                            const T* __restrict__ dy, T* __restrict__ dw, int chunks_per_split) {
+    simt_backward_weight_body<T, D, DEFORM>(blockIdx, g, x, off, dy, dw, chunks_per_split);
+}
+
+// Both backward passes in one launch, for problems so small that the launch itself is what they cost: the first
+// gd.x * gd.y blocks are the blocks of the data pass, the others those of the weight pass (fp32: the two bodies'
+// static shared memory together stays under 48 KB).
+template <int D, bool DEFORM>
+__global__ void __launch_bounds__(kThreads)
+simt_backward_both_kernel(const Geom g, const float* __restrict__ x, const float* __restrict__ off,
+                          const float* __restrict__ w, const float* __restrict__ dy, float* __restrict__ dx,
+                          float* __restrict__ doff, float* __restrict__ dw, const uint3 gd, const uint3 gw,
+                          int chunks_per_split) {
+    const unsigned nd = gd.x * gd.y;
+    if (blockIdx.x < nd) {
+        simt_backward_data_body<float, D, DEFORM>(make_uint3(blockIdx.x % gd.x, blockIdx.x / gd.x, 0), g, x, off, w, dy,
+                                                  dx, doff);
+    } else {
+        const unsigned r = blockIdx.x - nd;
+        simt_backward_weight_body<float, D, DEFORM>(make_uint3(r % gw.x, (r / gw.x) % gw.y, r / (gw.x * gw.y)), g, x, off,
+                                                    dy, dw, chunks_per_split);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 bias_grad_kernel(const Geom g, const T* __restrict__ dy, T* __restrict__ dbias) {
@@ -503,28 +538,68 @@ int launch_backward_data(const Geom& g, const void* x, const void* off, const vo
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-template <typename T, int D, bool DEFORM>
-int launch_backward_weight(const Geom& g, const void* x, const void* off, const void* dy, void* dw,
-                           cudaStream_t st) {
+// Work split of the weight pass: (grid, position chunks per split).
+inline void weight_grid(const Geom& g, dim3& grid, int& cps) {
     const long long chunks = (g.P + 15) / 16;
     const long long tiles = (long long)((g.Kg + 63) / 64) * g.G * ((g.Og + 63) / 64);
-    // aim for ~8 CTAs per SM overall, at least 8 chunks per split
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 148;
-    long long splits = ((long long)sms * 8 + tiles - 1) / tiles;
+    long long splits = ((long long)sms * 8 + tiles - 1) / tiles;      // ~8 CTAs per SM overall, >= 8 chunks per split
     if (splits > chunks / 8) splits = chunks / 8;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;
-    const int cps = (int)((chunks + splits - 1) / splits);
+    cps = (int)((chunks + splits - 1) / splits);
     splits = (chunks + cps - 1) / cps;
-    dim3 grid((unsigned)((g.Kg + 63) / 64), (unsigned)(g.G * ((g.Og + 63) / 64)), (unsigned)splits);
+    grid = dim3((unsigned)((g.Kg + 63) / 64), (unsigned)(g.G * ((g.Og + 63) / 64)), (unsigned)splits);
+}
+
+template <typename T, int D, bool DEFORM>
+int launch_backward_weight(const Geom& g, const void* x, const void* off, const void* dy, void* dw,
+                           cudaStream_t st) {
+    dim3 grid;
+    int cps;
+    weight_grid(g, grid, cps);
     simt_backward_weight_kernel<T, D, DEFORM><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off,
                                                                          (const T*)dy, (T*)dw, cps);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+template <int D, bool DEFORM>
+int launch_backward_both(const Geom& g, const float* x, const float* off, const float* w, const float* dy, float* dx,
+                         float* doff, float* dw, cudaStream_t st) {
+    const dim3 gd((unsigned)((g.P + 63) / 64), (unsigned)(g.G * ((g.Kg + 63) / 64)));
+    dim3 gw;
+    int cps;
+    weight_grid(g, gw, cps);
+    const unsigned total = gd.x * gd.y + gw.x * gw.y * gw.z;
+    simt_backward_both_kernel<D, DEFORM><<<total, kThreads, 0, st>>>(g, x, off, w, dy, dx, doff, dw,
+                                                                     make_uint3(gd.x, gd.y, 1), make_uint3(gw.x, gw.y, gw.z), cps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 }  // namespace
+
+// fp32 problems whose two backward grids together stay small take one launch for both passes (all outputs must be
+// wanted and zero-filled by the caller, as for the separate launchers).
+bool simt_backward_both_supported(const Geom& g, int dtype) {
+    if (dtype != 0) return false;
+    const long long nd = ((g.P + 63) / 64) * (long long)g.G * ((g.Kg + 63) / 64);
+    return nd <= 4096;
+}
+
+int simt_backward_both(const Geom& g, int ndim, int deform, const void* x, const void* off, const void* w,
+                       const void* dy, void* dx, void* doff, void* dw, cudaStream_t st) {
+    const float *xf = (const float*)x, *of = (const float*)off, *wf = (const float*)w, *dyf = (const float*)dy;
+    float *dxf = (float*)dx, *dof = (float*)doff, *dwf = (float*)dw;
+    if (deform && doff != nullptr &&
+        cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * ndim * g.ov * sizeof(float), st) != cudaSuccess)
+        return -5;
+    if (ndim == 2) return deform ? launch_backward_both<2, true>(g, xf, of, wf, dyf, dxf, dof, dwf, st)
+                                 : launch_backward_both<2, false>(g, xf, of, wf, dyf, dxf, dof, dwf, st);
+    return deform ? launch_backward_both<3, true>(g, xf, of, wf, dyf, dxf, dof, dwf, st)
+                  : launch_backward_both<3, false>(g, xf, of, wf, dyf, dxf, dof, dwf, st);
+}
 
 #define DCN_DISPATCH(FN, ...)                                                                     \
     do {                                                                                          \

@@ -123,8 +123,11 @@ pack_weight_slab(const Geom g, const __nv_bfloat16* __restrict__ wt, uint8_t* __
 // Sampling points, located once for all channel slabs of a deformable group.  One 16-byte entry per (sample,
 // deformable group, tap, output position), positions contiguous:
 //   x  bits 0-19 byte offset of the (lo_h, lo_w) pixel in the blocked dX plane | bits 27-28 its class
-//      | bit 29 hi_w != lo_w | bit 30 hi_h != lo_h | bit 31 valid        (0 for an invalid point)
+//      | bit 29 hi_w != lo_w | bit 30 hi_h != lo_h | bit 31 valid
 //   y  lo_h * Wp + lo_w (pixel index in the linear x plane)      z, w  the fractions lw_h, lw_w (fp32 bits)
+// An invalid point has bits 29-31 and the fractions zero and names some pixel inside the plane (the tap's
+// undeformed position, clamped): the kernel adds zeros there, and spreading those zeros over the plane keeps
+// them from colliding on one address.
 // The point is located exactly as everywhere else in the library (locate: int32 base + offset in one fp32
 // rounding, validity, truncation, edge rule); dcn_debug_tc_points decodes these entries for the bit-exactness test.
 __global__ void __launch_bounds__(256)
@@ -140,15 +143,20 @@ b2_points_kernel(const Geom g, const float* __restrict__ off, uint4* __restrict_
         Pt<float, 2> s;
         locate<float, 2>(g, offset_block<float, 2>(g, off, (int)n), (int)grp, (int)tap, op, s);
         uint4 r = make_uint4(0u, 0u, 0u, 0u);
+        int h0, w0;
         if (s.valid) {
-            const int h0 = s.lo[0], w0 = s.lo[1];
-            const uint32_t cls = (uint32_t)((h0 & 1) * 2 + (w0 & 1));
-            r.x = (uint32_t)(((h0 >> 1) * W2 + (w0 >> 1)) * 128) + cls * 32u;
-            r.x |= (cls << 27) | ((s.hi[1] != w0 ? 1u : 0u) << 29) | ((s.hi[0] != h0 ? 1u : 0u) << 30) | (1u << 31);
-            r.y = (uint32_t)(h0 * Wp + w0);
+            h0 = s.lo[0];
+            w0 = s.lo[1];
+            r.x = ((s.hi[1] != w0 ? 1u : 0u) << 29) | ((s.hi[0] != h0 ? 1u : 0u) << 30) | (1u << 31);
             r.z = __float_as_uint(s.lw[0]);
             r.w = __float_as_uint(s.lw[1]);
+        } else {
+            h0 = op.base[1] < 0 ? 0 : (op.base[1] >= g.in[1] ? g.in[1] - 1 : op.base[1]);
+            w0 = op.base[2] < 0 ? 0 : (op.base[2] >= g.in[2] ? g.in[2] - 1 : op.base[2]);
         }
+        const uint32_t cls = (uint32_t)((h0 & 1) * 2 + (w0 & 1));
+        r.x |= (uint32_t)(((h0 >> 1) * W2 + (w0 >> 1)) * 128) + cls * 32u + (cls << 27);
+        r.y = (uint32_t)(h0 * Wp + w0);
         pts[e] = r;
     }
 }
