@@ -44,11 +44,12 @@ METRIC = "deform_conv_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 
 # (config, pass) -> (dram__bytes_read.sum + dram__bytes_write.sum of the pass's main kernel in one ncu capture,
-# output positions of the captured launch).  Figures and commands: profiles/tc_*_cfg2_*.md.
+# output positions of the captured launch).  Figures and commands: profiles/tc_bwd2d_kernel_cfg2.md and
+# profiles/tc_forward_wgrad_kernels_cfg2_batch16.md (batch 16: a working set larger than L2).
 NCU_DRAM_BYTES = {
-    (2, "forward"): (117862400, 25088),
-    (2, "backward_data"): (67954688, 25088),
-    (2, "backward_weight"): (40454912, 25088),
+    (2, "forward"): (41422336 + 3489280, 50176),
+    (2, "backward_data"): (96318976 + 25689344, 50176),
+    (2, "backward_weight"): (68251392 + 1722112, 50176),
 }
 
 
