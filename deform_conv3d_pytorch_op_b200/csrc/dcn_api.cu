@@ -133,7 +133,8 @@ int dcn_launch_count(const dcn_problem* p, int pass) {
     Geom g;
     make_geom(p, g);
     if (p->precision == DCN_PREC_EXACT)
-        return (pass == DCN_PASS_BACKWARD && !dcn::simt_backward_both_supported(g, p->dtype)) ? 2 : 1;
+        return (pass == DCN_PASS_BACKWARD && !dcn::simt_backward_both_supported(g, p->dtype) &&
+                !dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable)) ? 2 : 1;
     if (!dcn::tc_supported(g, p->ndim, p->deformable)) return 0;
     return dcn::tc_launch_count(g, p->ndim, p->deformable, pass);
 }
@@ -154,6 +155,8 @@ int dcn_forward(const dcn_problem* p, const void* x, const void* offset, const v
         return dcn::tc_forward(g, p->ndim, p->deformable, (const float*)x, (const float*)offset,
                                (const float*)weight, (const float*)bias, (float*)y, ws, ws_bytes, st);
     }
+    if (dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable))
+        return dcn::simt_small_forward(g, p->ndim, x, offset, weight, bias, y, st);
     return dcn::simt_forward(g, p->dtype, p->ndim, p->deformable, x, offset, weight, bias, y, st);
 }
 
@@ -254,7 +257,9 @@ int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const 
             if (dweight != nullptr && cudaMemsetAsync(dweight, 0, (size_t)g.O * g.Cg * g.kv * es, st) != cudaSuccess)
                 return DCN_ERR_CUDA;
             const bool all = dx != nullptr && dweight != nullptr && (!p->deformable || doffset != nullptr);
-            if (all && dcn::simt_backward_both_supported(g, p->dtype)) {
+            if (dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable)) {
+                r = dcn::simt_small_backward(g, p->ndim, x, offset, weight, dy, dx, doffset, dweight, st);   // one launch
+            } else if (all && dcn::simt_backward_both_supported(g, p->dtype)) {
                 r = dcn::simt_backward_both(g, p->ndim, p->deformable, x, offset, weight, dy, dx,
                                             p->deformable ? doffset : nullptr, dweight, st);     // one launch
             } else {

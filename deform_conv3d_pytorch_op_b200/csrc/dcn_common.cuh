@@ -87,20 +87,15 @@ __device__ __forceinline__ void decompose_tap(const Geom& g, int tap, int t[3]) 
     t[0] = (int)tl; t[1] = (int)th; t[2] = (int)tw;
 }
 
-// Locate one sampling point from its D offset values (axis order (l,) h, w).
+// Validity, corners and weights of a point whose coordinates s.p are set (the reference's rule, see the top of
+// this file).
 template <typename T, int D>
-__device__ __forceinline__ void locate_with(const Geom& g, const T (&offv)[D], int tap, const OutPos& op,
-                                            Pt<T, D>& s) {
-    int t[3];
-    decompose_tap(g, tap, t);
+__device__ __forceinline__ void finish_point(const Geom& g, Pt<T, D>& s) {
     bool ok = true;
 #pragma unroll
     for (int a = 0; a < D; ++a) {
         const int ax = a + (3 - D);
-        const int ib = op.base[ax] + t[ax] * g.dil[ax];
-        const T pd = (T)ib + offv[a];                            // single rounding, no multiply
-        s.p[a] = pd;
-        ok = ok && (pd > (T)-1) && (pd < (T)g.in[ax]);
+        ok = ok && (s.p[a] > (T)-1) && (s.p[a] < (T)g.in[ax]);
     }
     s.valid = ok;
     if (ok) {
@@ -116,6 +111,21 @@ __device__ __forceinline__ void locate_with(const Geom& g, const T (&offv)[D], i
             s.hw[a] = (T)1 - s.lw[a];
         }
     }
+}
+
+// Locate one sampling point from its D offset values (axis order (l,) h, w).
+template <typename T, int D>
+__device__ __forceinline__ void locate_with(const Geom& g, const T (&offv)[D], int tap, const OutPos& op,
+                                            Pt<T, D>& s) {
+    int t[3];
+    decompose_tap(g, tap, t);
+#pragma unroll
+    for (int a = 0; a < D; ++a) {
+        const int ax = a + (3 - D);
+        const int ib = op.base[ax] + t[ax] * g.dil[ax];
+        s.p[a] = (T)ib + offv[a];                                 // single rounding, no multiply
+    }
+    finish_point<T, D>(g, s);
 }
 
 // Address of the first offset component of (grp, tap) at this output position; components are ov apart.

@@ -16,6 +16,12 @@ int simt_backward_data(const Geom& g, int dtype, int ndim, int deform, const voi
                        const void* w, const void* dy, void* dx, void* doff, cudaStream_t st);
 int simt_backward_weight(const Geom& g, int dtype, int ndim, int deform, const void* x, const void* off,
                          const void* dy, void* dw, cudaStream_t st);
+// latency-shaped kernels for very small fp32 deformable problems (dcn_simt_small.cuh)
+bool simt_small_supported(const Geom& g, int dtype, int ndim, int deform);
+int simt_small_forward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* bias,
+                       void* y, cudaStream_t st);
+int simt_small_backward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* dy,
+                        void* dx, void* doff, void* dw, cudaStream_t st);
 bool simt_backward_both_supported(const Geom& g, int dtype);
 int simt_backward_both(const Geom& g, int ndim, int deform, const void* x, const void* off, const void* w,
                        const void* dy, void* dx, void* doff, void* dw, cudaStream_t st);

@@ -578,7 +578,23 @@ int launch_backward_both(const Geom& g, const float* x, const float* off, const 
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+#include "dcn_simt_small.cuh"
+
 }  // namespace
+
+bool simt_small_supported(const Geom& g, int dtype, int ndim, int deform) { return small_supported(g, dtype, ndim, deform); }
+
+int simt_small_forward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* bias,
+                       void* y, cudaStream_t st) {
+    if (ndim == 2) return launch_small_forward<2>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)bias, (float*)y, st);
+    return launch_small_forward<3>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)bias, (float*)y, st);
+}
+
+int simt_small_backward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* dy,
+                        void* dx, void* doff, void* dw, cudaStream_t st) {
+    if (ndim == 2) return launch_small_backward<2>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)dy, (float*)dx, (float*)doff, (float*)dw, st);
+    return launch_small_backward<3>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)dy, (float*)dx, (float*)doff, (float*)dw, st);
+}
 
 // fp32 problems whose two backward grids together stay small take one launch for both passes (all outputs must be
 // wanted and zero-filled by the caller, as for the separate launchers).

@@ -1,0 +1,300 @@
+// Exact fp32 kernels for problems so small that latency, not throughput, is what they cost (included by
+// dcn_simt.cu inside its anonymous namespace).  A problem like N=2, 16->32 channels, 32x32 (57 MFLOP per step) has
+// a roofline time below one kernel launch; the tiled kernels spend ~25 us on it because a few CTAs walk the K loop
+// with a dependent offset -> corner -> FMA chain per chunk.  Here a CTA takes kSmallTP output positions of one
+// convolution group and does each phase once for all of K, every phase spread over all 256 threads:
+//   forward    weights of the group -> shared; sampling points; sampled patch [TP][Kg] -> shared; y = W * patch
+//   backward   (one launch for dX, dOffset and dW)  weights, dy tile, points -> shared;
+//              col = W^T dy per (position, k), consumed at once by the input-gradient scatter, the
+//              offset-gradient sum (shared-memory accumulators) and the recomputed patch; dW += dy * patch^T
+// Same arithmetic rules as the tiled kernels: locate / finish_point, interp, corner_weights, interp_grad, oob_term.
+#pragma once
+
+constexpr int kSmallThreads = 1024;      // one CTA per SM, eight warps per scheduler: the phases are latency chains
+
+struct SmallDims {
+    int TP;          // output positions per CTA
+    int ndg;         // deformable groups a convolution group's channels touch
+    int smem_fwd, smem_bwd;
+};
+
+// deformable groups overlapping the channels [j*Cg, (j+1)*Cg): first index and count
+__host__ __device__ inline void small_dg_range(const Geom& g, int j, int& grp0, int& n) {
+    grp0 = (j * g.Cg) / g.cpg;
+    n = ((j + 1) * g.Cg - 1) / g.cpg - grp0 + 1;
+}
+
+inline SmallDims small_dims(const Geom& g, int D) {
+    SmallDims d;
+    d.ndg = 1;
+    for (int j = 0; j < g.G; ++j) {
+        int g0, n;
+        small_dg_range(g, j, g0, n);
+        if (n > d.ndg) d.ndg = n;
+    }
+    d.TP = 16;
+    auto fwd = [&](int tp) { return 4 * (g.Og * g.Kg + tp * (g.Kg + 1) + tp * g.kv * d.ndg * (D + 1)); };
+    auto bwd = [&](int tp) {
+        return 4 * (g.Og * g.Kg + g.Og * tp + tp * (g.Kg + 1) + tp * g.kv * d.ndg * (D + 1) + tp * g.kv * d.ndg * D);
+    };
+    // within shared memory, and enough CTAs to reach most SMs where the problem has the positions for it
+    while (d.TP > 4 && (bwd(d.TP) > 96 * 1024 || (g.P + d.TP - 1) / d.TP * g.G < 96)) d.TP /= 2;
+    d.smem_fwd = fwd(d.TP);
+    d.smem_bwd = bwd(d.TP);
+    return d;
+}
+
+// One sampling point per (position of the tile, tap, deformable group of the conv group): its D coordinates
+// and a validity word, positions fastest so that the offset loads coalesce.
+template <int D>
+__device__ __forceinline__ void small_points(const Geom& g, const float* __restrict__ off, int j, int TP, int ndg,
+                                             long long P0, float* __restrict__ pts) {
+    int grp0, n_;
+    small_dg_range(g, j, grp0, n_);
+    for (int e = threadIdx.x; e < TP * g.kv * ndg; e += kSmallThreads) {
+        const int pl = e % TP, r = e / TP, tap = r % g.kv, gl = r / g.kv;
+        float* dst = pts + (size_t)e * (D + 1);
+        const long long P = P0 + pl;
+        bool ok = false;
+        if (P < g.P && gl < n_) {
+            const OutPos op = decompose_pos(g, P);
+            Pt<float, D> s;
+            locate<float, D>(g, offset_block<float, D>(g, off, op.n), grp0 + gl, tap, op, s);
+#pragma unroll
+            for (int a = 0; a < D; ++a) dst[a] = s.p[a];
+            ok = true;
+        }
+        dst[D] = ok ? 1.f : 0.f;
+    }
+}
+
+// The point of entry e as the tiled kernels would have located it (same finish_point).
+template <int D>
+__device__ __forceinline__ bool small_load_point(const Geom& g, const float* __restrict__ pts, int e, Pt<float, D>& s) {
+    const float* src = pts + (size_t)e * (D + 1);
+    if (src[D] == 0.f) { s.valid = false; return false; }
+#pragma unroll
+    for (int a = 0; a < D; ++a) s.p[a] = src[a];
+    finish_point<float, D>(g, s);
+    return true;                                         // the position exists (the point may still be invalid)
+}
+
+template <int D>
+__global__ void __launch_bounds__(kSmallThreads)
+small_forward_kernel(const Geom g, const float* __restrict__ x, const float* __restrict__ off,
+                     const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ y,
+                     const int TP, const int ndg) {
+    extern __shared__ float sm_small[];
+    float* Ws = sm_small;                                 // [Og][Kg]
+    float* smp = Ws + g.Og * g.Kg;                        // [TP][Kg + 1]
+    float* pts = smp + TP * (g.Kg + 1);                   // [ndg][kv][TP][D + 1]
+    const int j = blockIdx.y;
+    const long long P0 = (long long)blockIdx.x * TP;
+    int grp0, n_;
+    small_dg_range(g, j, grp0, n_);
+    for (int i = threadIdx.x; i < g.Og * g.Kg; i += kSmallThreads) Ws[i] = __ldg(w + (size_t)j * g.Og * g.Kg + i);
+    small_points<D>(g, off, j, TP, ndg, P0, pts);
+    __syncthreads();
+    // (unrolled so that the corner loads of several items are in flight together: the phase is one round of
+    // global-memory latency, not one per item)
+#pragma unroll 4
+    for (int it = threadIdx.x; it < TP * g.Kg; it += kSmallThreads) {
+        const int pl = it % TP, k = it / TP;
+        uint32_t cl, tap;
+        g.d_kv.divmod((uint32_t)k, cl, tap);
+        const int c = j * g.Cg + (int)cl;
+        const int gl = (int)g.d_cpg.div((uint32_t)c) - grp0;
+        Pt<float, D> s;
+        float val = 0.f;
+        if (small_load_point<D>(g, pts, (gl * g.kv + (int)tap) * TP + pl, s) && s.valid) {
+            uint32_t n = g.d_ov.div((uint32_t)(P0 + pl));
+            const float* plane = x + ((size_t)n * g.C + c) * g.iv;
+            int idx[1 << D];
+            corner_indices<float, D>(g, s, idx);
+            float cv[1 << D];
+#pragma unroll
+            for (int i = 0; i < (1 << D); ++i) cv[i] = __ldg(plane + idx[i]);
+            val = interp<float, D>(s, cv);
+        }
+        smp[pl * (g.Kg + 1) + k] = val;
+    }
+    __syncthreads();
+    // y = W * patch: S adjacent lanes share one output and split K among them (S a power of two that divides 32)
+    const int outs = TP * g.Og;
+    int S = 1;
+    while (S < 8 && outs * (S * 2) <= kSmallThreads) S *= 2;
+    for (int base = 0; base < outs * S; base += kSmallThreads) {
+        const int t = base + (int)threadIdx.x;
+        const int it = t / S, sub = t % S;
+        const bool live = it < outs;
+        const int pl = live ? it % TP : 0, ol = live ? it / TP : 0;
+        const float* wr = Ws + ol * g.Kg;
+        const float* sr = smp + pl * (g.Kg + 1);
+        float a2[2] = {0.f, 0.f};
+        int k = sub;
+        for (; k + S < g.Kg; k += 2 * S) {
+            a2[0] = fmaf(wr[k], sr[k], a2[0]);
+            a2[1] = fmaf(wr[k + S], sr[k + S], a2[1]);
+        }
+        if (k < g.Kg) a2[0] = fmaf(wr[k], sr[k], a2[0]);
+        float acc = a2[0] + a2[1];
+        for (int m = S / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        const long long P = P0 + pl;
+        if (!live || sub != 0 || P >= g.P) continue;
+        uint32_t n, opos;
+        g.d_ov.divmod((uint32_t)P, n, opos);
+        const int o = j * g.Og + ol;
+        y[((size_t)n * g.O + o) * g.ov + opos] = acc + (bias != nullptr ? __ldg(bias + o) : 0.f);
+    }
+}
+
+// dx and dw must be zero-filled by the caller; doff is written with plain stores when DOFF_PLAIN (one conv group:
+// a CTA then holds every channel of the deformable groups it touches), else added to a zero-filled doff.
+template <int D, bool DOFF_PLAIN>
+__global__ void __launch_bounds__(kSmallThreads)
+small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __restrict__ off,
+                      const float* __restrict__ w, const float* __restrict__ dy, float* __restrict__ dx,
+                      float* __restrict__ doff, float* __restrict__ dw, const int TP, const int ndg) {
+    extern __shared__ float sm_small[];
+    float* Ws = sm_small;                                 // [Og][Kg]
+    float* dys = Ws + g.Og * g.Kg;                        // [Og][TP]
+    float* smp = dys + g.Og * TP;                         // [TP][Kg + 1]
+    float* pts = smp + TP * (g.Kg + 1);                   // [ndg][kv][TP][D + 1]
+    float* dacc = pts + TP * g.kv * ndg * (D + 1);        // [ndg][kv][TP][D]
+    const int j = blockIdx.y;
+    const long long P0 = (long long)blockIdx.x * TP;
+    int grp0, n_;
+    small_dg_range(g, j, grp0, n_);
+    for (int i = threadIdx.x; i < g.Og * g.Kg; i += kSmallThreads) Ws[i] = __ldg(w + (size_t)j * g.Og * g.Kg + i);
+    for (int i = threadIdx.x; i < g.Og * TP; i += kSmallThreads) {
+        const int pl = i % TP, ol = i / TP;
+        const long long P = P0 + pl;
+        float v = 0.f;
+        if (P < g.P) {
+            uint32_t n, opos;
+            g.d_ov.divmod((uint32_t)P, n, opos);
+            v = __ldg(dy + ((size_t)n * g.O + j * g.Og + ol) * g.ov + opos);
+        }
+        dys[ol * TP + pl] = v;
+    }
+    for (int i = threadIdx.x; i < TP * g.kv * ndg * D; i += kSmallThreads) dacc[i] = 0.f;
+    small_points<D>(g, off, j, TP, ndg, P0, pts);
+    __syncthreads();
+#pragma unroll 2
+    for (int it = threadIdx.x; it < TP * g.Kg; it += kSmallThreads) {
+        const int pl = it % TP, k = it / TP;
+        uint32_t cl, tap;
+        g.d_kv.divmod((uint32_t)k, cl, tap);
+        const int c = j * g.Cg + (int)cl;
+        const int gl = (int)g.d_cpg.div((uint32_t)c) - grp0;
+        const int e = (gl * g.kv + (int)tap) * TP + pl;
+        Pt<float, D> s;
+        float val = 0.f;
+        if (small_load_point<D>(g, pts, e, s)) {
+            float c4[4] = {0.f, 0.f, 0.f, 0.f};
+            int ol = 0;
+            for (; ol + 4 <= g.Og; ol += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) c4[u] = fmaf(Ws[(ol + u) * g.Kg + k], dys[(ol + u) * TP + pl], c4[u]);
+            }
+            for (; ol < g.Og; ++ol) c4[0] = fmaf(Ws[ol * g.Kg + k], dys[ol * TP + pl], c4[0]);
+            const float col = (c4[0] + c4[1]) + (c4[2] + c4[3]);
+            if (s.valid) {
+                const uint32_t n = g.d_ov.div((uint32_t)(P0 + pl));
+                const size_t pbase = ((size_t)n * g.C + c) * g.iv;
+                int idx[1 << D];
+                corner_indices<float, D>(g, s, idx);
+                float cv[1 << D];
+#pragma unroll
+                for (int i = 0; i < (1 << D); ++i) cv[i] = __ldg(x + pbase + idx[i]);
+                val = interp<float, D>(s, cv);
+                if (dx != nullptr) {
+                    float cw[1 << D];
+                    corner_weights<float, D>(s, cw);
+#pragma unroll
+                    for (int i = 0; i < (1 << D); ++i) atomicAdd(dx + pbase + idx[i], cw[i] * col);
+                }
+                if (doff != nullptr) {
+                    float gr[D];
+                    interp_grad<float, D>(s, cv, gr);
+#pragma unroll
+                    for (int a = 0; a < D; ++a) atomicAdd(dacc + (size_t)e * D + a, col * gr[a]);
+                }
+            } else if (D == 3 && g.oob && doff != nullptr) {
+#pragma unroll
+                for (int a = 0; a < D; ++a) {
+                    const float t = oob_term<float>(g, s.p[a], col);
+                    if (t != 0.f) atomicAdd(dacc + (size_t)e * D + a, t);
+                }
+            }
+        }
+        smp[pl * (g.Kg + 1) + k] = val;
+    }
+    __syncthreads();
+    if (dw != nullptr) {
+        for (int it = threadIdx.x; it < g.Og * g.Kg; it += kSmallThreads) {
+            const int k = it % g.Kg, ol = it / g.Kg;
+            float a2[2] = {0.f, 0.f};
+            for (int pl = 0; pl < TP; pl += 2) {           // TP is even
+                a2[0] = fmaf(dys[ol * TP + pl], smp[pl * (g.Kg + 1) + k], a2[0]);
+                a2[1] = fmaf(dys[ol * TP + pl + 1], smp[(pl + 1) * (g.Kg + 1) + k], a2[1]);
+            }
+            const float acc = a2[0] + a2[1];
+            if (acc != 0.f) atomicAdd(dw + ((size_t)j * g.Og + ol) * g.Kg + k, acc);
+        }
+    }
+    if (doff != nullptr) {
+        for (int i = threadIdx.x; i < TP * g.kv * ndg * D; i += kSmallThreads) {
+            const int a = i % D, e = i / D;
+            const int pl = e % TP, r = e / TP, tap = r % g.kv, gl = r / g.kv;
+            const long long P = P0 + pl;
+            if (P >= g.P || gl >= n_) continue;
+            uint32_t n, opos;
+            g.d_ov.divmod((uint32_t)P, n, opos);
+            float* dst = doff + ((size_t)n * g.dg * g.kv * D + (size_t)((grp0 + gl) * g.kv + tap) * D + a) * g.ov + opos;
+            if (DOFF_PLAIN) *dst = dacc[i];
+            else if (dacc[i] != 0.f) atomicAdd(dst, dacc[i]);
+        }
+    }
+}
+
+// fp32 deformable problems of at most 2^24 multiply-adds per pass whose group weights fit the shared memory.
+inline bool small_supported(const Geom& g, int dtype, int ndim, int deform) {
+    if (dtype != 0 || !deform) return false;
+    if ((double)g.P * g.Kg * g.Og * g.G > 16777216.0) return false;
+    const SmallDims d = small_dims(g, ndim);
+    return d.smem_bwd <= 96 * 1024 && d.smem_fwd <= 96 * 1024;
+}
+
+template <int D>
+int launch_small_forward(const Geom& g, const float* x, const float* off, const float* w, const float* bias, float* y,
+                         cudaStream_t st) {
+    const SmallDims d = small_dims(g, D);
+    auto kern = small_forward_kernel<D>;
+    if (d.smem_fwd > 48 * 1024 &&
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_fwd) != cudaSuccess) return -5;
+    dim3 grid((unsigned)((g.P + d.TP - 1) / d.TP), (unsigned)g.G);
+    kern<<<grid, kSmallThreads, d.smem_fwd, st>>>(g, x, off, w, bias, y, d.TP, d.ndg);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+template <int D>
+int launch_small_backward(const Geom& g, const float* x, const float* off, const float* w, const float* dy, float* dx,
+                          float* doff, float* dw, cudaStream_t st) {
+    const SmallDims d = small_dims(g, D);
+    dim3 grid((unsigned)((g.P + d.TP - 1) / d.TP), (unsigned)g.G);
+    if (g.G == 1) {
+        auto kern = small_backward_kernel<D, true>;
+        if (d.smem_bwd > 48 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
+        kern<<<grid, kSmallThreads, d.smem_bwd, st>>>(g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
+    } else {
+        if (doff != nullptr &&
+            cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * D * g.ov * sizeof(float), st) != cudaSuccess) return -5;
+        auto kern = small_backward_kernel<D, false>;
+        if (d.smem_bwd > 48 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
+        kern<<<grid, kSmallThreads, d.smem_bwd, st>>>(g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
