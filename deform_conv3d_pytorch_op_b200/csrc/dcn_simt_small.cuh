@@ -2,7 +2,7 @@
 // dcn_simt.cu inside its anonymous namespace).  A problem like N=2, 16->32 channels, 32x32 (57 MFLOP per step) has
 // a roofline time below one kernel launch; the tiled kernels spend ~25 us on it because a few CTAs walk the K loop
 // with a dependent offset -> corner -> FMA chain per chunk.  Here a CTA takes kSmallTP output positions of one
-// convolution group and does each phase once for all of K, every phase spread over all 256 threads:
+// convolution group and does each phase once for all of K, every phase spread over all 1024 threads:
 //   forward    weights of the group -> shared; sampling points; sampled patch [TP][Kg] -> shared; y = W * patch
 //   backward   (one launch for dX, dOffset and dW)  weights, dy tile, points -> shared;
 //              col = W^T dy per (position, k), consumed at once by the input-gradient scatter, the

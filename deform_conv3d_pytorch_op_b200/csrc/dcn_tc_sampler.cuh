@@ -161,6 +161,22 @@ template <int D, bool DEFORM>
 __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 << D) : 1],
                                                  const float (&w)[DEFORM ? (1 << D) : 1]) {
     if constexpr (!DEFORM) return q[0];
+#ifdef DCN_INTERP_BF16X2
+    else {
+        uint32_t acc[4];
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            const uint32_t w2 = pack_bf16x2(w[c], w[c]);
+            const uint32_t wd[4] = {q[c].x, q[c].y, q[c].z, q[c].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (c == 0) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(acc[i]) : "r"(w2), "r"(wd[i]));
+                else asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(acc[i]) : "r"(w2), "r"(wd[i]), "r"(acc[i]));
+            }
+        }
+        return make_uint4(acc[0], acc[1], acc[2], acc[3]);
+    }
+#else
     else {
         uint64_t acc[4];
 #pragma unroll
@@ -182,4 +198,5 @@ __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 <<
         }
         return make_uint4(out[0], out[1], out[2], out[3]);
     }
+#endif
 }
