@@ -310,6 +310,123 @@ int dcn_debug_expire_wait(int32_t* gave_up, void* stream) {
 int dcn_check_status(void* stream) { return dcn::tc_check_status(static_cast<cudaStream_t>(stream)); }
 
 // ------------------------------------------------------------------------------------------------
+// Deformable layer: offset-producing convolution + deformable convolution of the same input
+// ------------------------------------------------------------------------------------------------
+int dcn_offset_conv_problem(const dcn_problem* p, dcn_problem* q) {
+    if (p == nullptr || q == nullptr) return DCN_ERR_NULL;
+    const int v = validate(p);
+    if (v != DCN_OK) return v;
+    if (!p->deformable) return DCN_ERR_UNSUPPORTED;
+    *q = *p;
+    int kv = 1;
+    for (int d = 0; d < 3; ++d) {
+        kv *= p->k[d];
+        q->dil[d] = 1;          // the deformable size rule ignores dilation: only dilation 1 gives the same output size
+    }
+    q->O = (p->C / p->cpg) * kv * p->ndim;
+    q->G = 1;
+    q->cpg = p->C;
+    q->deformable = 0;
+    q->std_size_rule = 1;
+    q->oob_offset_grad = 0;
+    q->channels_last = 0;       // offsets are [N, dg*kv*D, out...] whatever the layout of x
+    return validate(q);
+}
+
+static size_t layer_doff_bytes(const dcn_problem* p, const Geom& g) {
+    const size_t es = p->dtype == DCN_F64 ? 8 : 4;
+    return ((size_t)g.N * g.dg * g.kv * p->ndim * g.ov * es + 255) / 256 * 256;
+}
+
+size_t dcn_layer_workspace_bytes(const dcn_problem* p, int pass) {
+    dcn_problem q;
+    if (dcn_offset_conv_problem(p, &q) != DCN_OK) return 0;
+    Geom g, gq;
+    make_geom(p, g);
+    make_geom(&q, gq);
+    if (p->precision == DCN_PREC_EXACT) return pass == DCN_PASS_FORWARD ? 0 : layer_doff_bytes(p, g);
+    if (!dcn::tc_supported(g, p->ndim, 1) || !dcn::tc_supported(gq, p->ndim, 0)) return 0;
+    return dcn::tc_layer_workspace_bytes(g, gq, p->ndim, pass == DCN_PASS_FORWARD ? 0 : 3);
+}
+
+int dcn_layer_forward(const dcn_problem* p, const void* x, const void* offset_weight, const void* offset_bias,
+                      const void* weight, const void* bias, void* offset, void* y, void* ws, size_t ws_bytes,
+                      void* stream) {
+    dcn_problem q;
+    const int v = dcn_offset_conv_problem(p, &q);
+    if (v != DCN_OK) return v;
+    if (x == nullptr || offset_weight == nullptr || weight == nullptr || offset == nullptr || y == nullptr)
+        return DCN_ERR_NULL;
+    const int a = check_ptrs(p, {x, offset_weight, offset_bias, weight, bias, offset, y});
+    if (a != DCN_OK) return a;
+    if (p->precision == DCN_PREC_EXACT) {
+        const int r = dcn_forward(&q, x, nullptr, offset_weight, offset_bias, offset, nullptr, 0, stream);
+        if (r != DCN_OK) return r;
+        return dcn_forward(p, x, offset, weight, bias, y, nullptr, 0, stream);
+    }
+    if (p->dtype != DCN_F32) return DCN_ERR_UNSUPPORTED;
+    Geom g, gq;
+    make_geom(p, g);
+    make_geom(&q, gq);
+    if (!dcn::tc_supported(g, p->ndim, 1) || !dcn::tc_supported(gq, p->ndim, 0)) return DCN_ERR_UNSUPPORTED;
+    if (!workspace_ok(ws, ws_bytes, dcn::tc_layer_workspace_bytes(g, gq, p->ndim, 0))) return DCN_ERR_WORKSPACE;
+    return dcn::tc_layer_forward(g, gq, p->ndim, (const float*)x, (const float*)offset_weight, (const float*)offset_bias,
+                                 (const float*)weight, (const float*)bias, (float*)offset, (float*)y, ws, ws_bytes,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int dcn_layer_backward(const dcn_problem* p, const void* x, const void* offset, const void* offset_weight,
+                       const void* weight, const void* dy, const void* x_channels_last, void* dx,
+                       void* doffset_weight, void* doffset_bias, void* dweight, void* dbias, void* ws, size_t ws_bytes,
+                       void* stream) {
+    dcn_problem q;
+    const int v = dcn_offset_conv_problem(p, &q);
+    if (v != DCN_OK) return v;
+    if (x == nullptr || offset == nullptr || offset_weight == nullptr || weight == nullptr || dy == nullptr)
+        return DCN_ERR_NULL;
+    const int a = check_ptrs(p, {x, offset, offset_weight, weight, dy, dx, doffset_weight, doffset_bias, dweight, dbias});
+    if (a != DCN_OK) return a;
+    Geom g, gq;
+    make_geom(p, g);
+    make_geom(&q, gq);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool chain = dx != nullptr || doffset_weight != nullptr || doffset_bias != nullptr;
+    if (p->precision == DCN_PREC_EXACT) {
+        if (chain && !workspace_ok(ws, ws_bytes, layer_doff_bytes(p, g))) return DCN_ERR_WORKSPACE;
+        void* doff = chain ? ws : nullptr;
+        int r = dcn_backward(p, x, offset, weight, dy, nullptr, dx, doff, dweight, dbias, nullptr, 0, stream);
+        if (r != DCN_OK || !chain) return r;
+        if (dx != nullptr) {                                            // accumulates into the dx just written
+            r = dcn_backward_data(&q, nullptr, nullptr, offset_weight, doff, dx, nullptr, nullptr, 0, stream);
+            if (r != DCN_OK) return r;
+        }
+        if (doffset_weight != nullptr) {
+            const size_t es = p->dtype == DCN_F64 ? 8 : 4;
+            if (cudaMemsetAsync(doffset_weight, 0, (size_t)gq.O * gq.Cg * gq.kv * es, st) != cudaSuccess) return DCN_ERR_CUDA;
+        }
+        if (doffset_weight != nullptr || doffset_bias != nullptr)
+            r = dcn_backward_weight(&q, x, nullptr, doff, doffset_weight, doffset_bias, nullptr, 0, stream);
+        return r;
+    }
+    if (p->dtype != DCN_F32) return DCN_ERR_UNSUPPORTED;
+    if (!dcn::tc_supported(g, p->ndim, 1) || !dcn::tc_supported(gq, p->ndim, 0)) return DCN_ERR_UNSUPPORTED;
+    if (!workspace_ok(ws, ws_bytes, dcn::tc_layer_workspace_bytes(g, gq, p->ndim, 3))) return DCN_ERR_WORKSPACE;
+    if (x_channels_last != nullptr && !aligned(x_channels_last, 16)) return DCN_ERR_ALIGN;
+    float* doff = nullptr;
+    int r = dcn::tc_layer_backward(g, gq, p->ndim, (const float*)x, (const float*)offset, (const float*)offset_weight,
+                                   (const float*)weight, (const float*)dy, x_channels_last, (float*)dx,
+                                   (float*)doffset_weight, (float*)dweight, doffset_bias != nullptr ? &doff : nullptr, ws,
+                                   ws_bytes, st);
+    if (r != DCN_OK) return r;
+    if (dbias != nullptr) {
+        r = dcn::bias_grad(g, p->dtype, dy, dbias, st);
+        if (r != DCN_OK) return r;
+    }
+    if (doffset_bias != nullptr) r = dcn::bias_grad(gq, p->dtype, doff, doffset_bias, st);
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Reference-named wrappers
 // ------------------------------------------------------------------------------------------------
 static dcn_problem make3d(int dtype, int N, int C, int L, int H, int W, int O, int kl, int kh, int kw, int pl, int ph,

@@ -42,6 +42,14 @@ size_t tc_backward_workspace_bytes(const Geom& g);
 int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
                 const float* dy, const void* xcl_in, float* dx, float* doff, float* dw, void* ws, size_t ws_bytes,
                 cudaStream_t st);
+// deformable layer = offset-producing plain convolution (gq) + deformable convolution (g) of the same input
+size_t tc_layer_workspace_bytes(const Geom& g, const Geom& gq, int ndim, int pass);
+int tc_layer_forward(const Geom& g, const Geom& gq, int ndim, const float* x, const float* w_off, const float* b_off,
+                     const float* w, const float* bias, float* offsets, float* y, void* ws, size_t ws_bytes,
+                     cudaStream_t st);
+int tc_layer_backward(const Geom& g, const Geom& gq, int ndim, const float* x, const float* offsets, const float* w_off,
+                      const float* w, const float* dy, const void* xcl_in, float* dx, float* dw_off, float* dw,
+                      float** doff_out, void* ws, size_t ws_bytes, cudaStream_t st);
 int tc_forward_static(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
                       const float* bias, float* y, cudaStream_t st);
 size_t tc_static_scratch_bytes();

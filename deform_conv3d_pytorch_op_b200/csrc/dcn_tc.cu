@@ -356,16 +356,22 @@ int tc_debug_points(const Geom& g, int ndim, int deform, const float* off, int n
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
-               const float* bias, float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+// `xcl_in`: a channels-last bf16 copy of x that already exists (the workspace's own copy is then not built).
+static int tc_forward_x(const Geom& g, int ndim, int deform, const float* x, const __nv_bfloat16* xcl_in, const float* off,
+                        const float* w, const float* bias, float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
     const FwdWorkspace l = fwd_workspace(g);
     if (ws_bytes < l.total) return -4;
     uint8_t* base = static_cast<uint8_t*>(ws);
-    __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+    const __nv_bfloat16* xcl = xcl_in;
     uint8_t* wpk = base + l.wpk_off;
     const TcDims d = tc_dims(g);
-    int r = launch_channels_last(g, x, xcl, st);
-    if (r != 0) return r;
+    int r = 0;
+    if (xcl == nullptr) {
+        __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+        r = launch_channels_last(g, x, mine, st);
+        if (r != 0) return r;
+        xcl = mine;
+    }
     __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(base + l.wt_off);
     r = launch_weight_to_kmajor(g, w, wt, nullptr, st);
     if (r != 0) return r;
@@ -375,6 +381,11 @@ int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float*
                                  : launch_tc_forward<2, false>(g, xcl, off, wpk, bias, y, st);
     return deform ? launch_tc_forward<3, true>(g, xcl, off, wpk, bias, y, st)
                   : launch_tc_forward<3, false>(g, xcl, off, wpk, bias, y, st);
+}
+
+int tc_forward(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
+               const float* bias, float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+    return tc_forward_x(g, ndim, deform, x, nullptr, off, w, bias, y, ws, ws_bytes, st);
 }
 
 int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const float* off, const float* w,
@@ -520,6 +531,104 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         if (r != 0) return r;
     }
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Deformable layer: the plain convolution that produces the offsets (geometry gq: same input, taps, stride and
+// padding, dilation 1, one group, dg*kv*D output channels, channel-first output whatever the layout of x)
+// followed by the deformable convolution (geometry g) of the same input.  One channels-last bf16 copy of x
+// serves both convolutions in the forward pass and all four gradient kernels in the backward pass; the offsets
+// are written once and read back while they are still in L2.
+// Workspaces: forward  [ forward workspace of g (its start holds the input copy) | forward workspace of gq ]
+//             backward [ dOffset | backward workspace of g | backward workspace of gq ]
+// ---------------------------------------------------------------------------------------------------
+static size_t layer_doff_bytes(const Geom& g, int ndim) {
+    return align_up((size_t)g.N * g.dg * g.kv * ndim * g.ov * sizeof(float), 256);
+}
+
+size_t tc_layer_workspace_bytes(const Geom& g, const Geom& gq, int ndim, int pass) {
+    if (pass == 0) return fwd_workspace(g).total + align_up(fwd_workspace(gq).total, 256);
+    return layer_doff_bytes(g, ndim) + align_up(bwd_data_workspace(g).total, 256) + align_up(bwd_data_workspace(gq).total, 256);
+}
+
+int tc_layer_forward(const Geom& g, const Geom& gq, int ndim, const float* x, const float* w_off, const float* b_off,
+                     const float* w, const float* bias, float* offsets, float* y, void* ws, size_t ws_bytes,
+                     cudaStream_t st) {
+    if (ws_bytes < tc_layer_workspace_bytes(g, gq, ndim, 0)) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    const size_t main_bytes = align_up(fwd_workspace(g).total, 256);
+    __nv_bfloat16* xcl = reinterpret_cast<__nv_bfloat16*>(base + fwd_workspace(g).xcl_off);
+    int r = launch_channels_last(g, x, xcl, st);
+    if (r != 0) return r;
+    r = tc_forward_x(gq, ndim, 0, x, xcl, nullptr, w_off, b_off, offsets, base + main_bytes, ws_bytes - main_bytes, st);
+    if (r != 0) return r;
+    return tc_forward_x(g, ndim, 1, x, xcl, offsets, w, bias, y, base, main_bytes, st);
+}
+
+// Gradients of the offset-producing convolution given dOffset: its input gradient is ADDED to dx (which the
+// deformable part has already written, in the layout of g), its weight gradient overwrites dw_off.
+static int plain_backward_into(const Geom& gq, int ndim, bool dx_channels_last, const __nv_bfloat16* xcl,
+                               const float* w_off, const float* dyq, float* dx, float* dw_off, void* ws,
+                               cudaStream_t st) {
+    const BwdDataWorkspace l = bwd_data_workspace(gq);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    uint8_t* dpk = base + l.dpk_off;
+    uint8_t* wpk = base + l.wpk_off;
+    const DgDims d = dg_dims(gq);
+    int r = launch_pack_dy(gq, dyq, dpk, d.MT, d.PC2, st);
+    if (r != 0) return r;
+    if (dx != nullptr) {
+        __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(base + l.wt_off);
+        r = launch_weight_to_kmajor(gq, w_off, wt, nullptr, st);
+        if (r != 0) return r;
+        pack_weight_bwd<<<gq.G * d.NB * d.OC, 256, 0, st>>>(gq, wt, wpk, d.NB, d.OC);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+        float* dxcl = dx_channels_last ? dx : reinterpret_cast<float*>(base + l.dxcl_off);
+        if (!dx_channels_last && cudaMemsetAsync(dxcl, 0, (size_t)gq.N * gq.iv * gq.C * 4, st) != cudaSuccess) return -5;
+        r = ndim == 2 ? launch_tc_dgrad<2, false>(gq, xcl, nullptr, dpk, wpk, dxcl, nullptr, st)
+                      : launch_tc_dgrad<3, false>(gq, xcl, nullptr, dpk, wpk, dxcl, nullptr, st);
+        if (r != 0) return r;
+        if (!dx_channels_last) {
+            dim3 grid((unsigned)((gq.iv + 31) / 32), (unsigned)((gq.C + 31) / 32), (unsigned)gq.N);
+            from_channels_last<true><<<grid, 256, 0, st>>>(dxcl, dx, gq.C, gq.iv);
+            if (cudaGetLastError() != cudaSuccess) return -5;
+        }
+    }
+    if (dw_off != nullptr) {
+        float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
+        r = dwpk_clear(gq, dwpk, st);
+        if (r != 0) return r;
+        r = ndim == 2 ? launch_tc_wgrad<2, false>(gq, xcl, nullptr, dpk, dwpk, st)
+                      : launch_tc_wgrad<3, false>(gq, xcl, nullptr, dpk, dwpk, st);
+        if (r != 0) return r;
+        r = dwpk_fold<false>(gq, dwpk, dw_off, st);
+        if (r != 0) return r;
+    }
+    return 0;
+}
+
+int tc_layer_backward(const Geom& g, const Geom& gq, int ndim, const float* x, const float* offsets, const float* w_off,
+                      const float* w, const float* dy, const void* xcl_in, float* dx, float* dw_off, float* dw,
+                      float** doff_out, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (ws_bytes < tc_layer_workspace_bytes(g, gq, ndim, 3)) return -4;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    float* doff = reinterpret_cast<float*>(base);
+    uint8_t* ws_main = base + layer_doff_bytes(g, ndim);
+    const size_t main_bytes = align_up(bwd_data_workspace(g).total, 256);
+    uint8_t* ws_q = ws_main + main_bytes;
+    const __nv_bfloat16* xcl = static_cast<const __nv_bfloat16*>(xcl_in);
+    if (xcl == nullptr) {
+        __nv_bfloat16* mine = reinterpret_cast<__nv_bfloat16*>(ws_main + bwd_data_workspace(g).xcl_off);
+        const int r0 = launch_channels_last(g, x, mine, st);
+        if (r0 != 0) return r0;
+        xcl = mine;
+    }
+    const bool chain = dx != nullptr || dw_off != nullptr || doff_out != nullptr;     // dOffset is needed downstream
+    int r = tc_backward(g, ndim, 1, x, offsets, w, dy, xcl, dx, chain ? doff : nullptr, dw, ws_main, main_bytes, st);
+    if (r != 0) return r;
+    if (doff_out != nullptr) *doff_out = doff;
+    if (dx == nullptr && dw_off == nullptr) return 0;
+    return plain_backward_into(gq, ndim, g.cl != 0, xcl, w_off, doff, dx, dw_off, ws_q, st);
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -231,6 +231,65 @@ class Op:
         _lib.check(st, "dcn_backward_weight")
         return dw, db
 
+    # -- deformable layer: offset-producing convolution + deformable convolution in one call -------------------
+    def offset_weight_shape(self):
+        """Weight shape of the convolution that produces this operator's offsets: [dg*kv*D, C, k...]."""
+        return (self.offset_channels, self.C) + tuple(self.weight_shape[2:])
+
+    def _layer_ws(self, which: int):
+        nbytes = _lib.lib().dcn_layer_workspace_bytes(ctypes.byref(self.p), which)
+        if nbytes == 0:
+            return None, 0
+        return torch.empty(nbytes, dtype=torch.uint8, device=self.device), nbytes
+
+    def layer_forward(self, x, offset_weight, offset_bias, weight, bias=None, keep_workspace: bool = False):
+        """offset = conv(x, offset_weight) + offset_bias; y = deform_conv(x, offset, weight) + bias.
+        Returns (y, offset[, workspace])."""
+        if not self.deformable:
+            raise DcnError("the layer entry points need a deformable operator")
+        x = self._act(x, "input")
+        weight = _prep(weight, "weight", x)
+        bias = _prep(bias, "bias", x)
+        offset_weight = _prep(offset_weight, "offset_weight", x)
+        offset_bias = _prep(offset_bias, "offset_bias", x)
+        if tuple(offset_weight.shape) != self.offset_weight_shape():
+            raise DcnError("offset_weight shape %s, expected %s" % (tuple(offset_weight.shape),
+                                                                    self.offset_weight_shape()))
+        y = self._new_act((self.N, self.O) + tuple(self.out_size), x)
+        offset = torch.empty((self.N, self.offset_channels) + tuple(self.out_size), dtype=x.dtype, device=x.device)
+        ws, nb = self._layer_ws(_lib.PASS_FORWARD)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dcn_layer_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset_weight),
+                                              _lib.ptr(offset_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(offset),
+                                              _lib.ptr(y), _lib.ptr(ws), nb, _lib.current_stream(x.device))
+        _lib.check(st, "dcn_layer_forward")
+        return (y, offset, ws) if keep_workspace else (y, offset)
+
+    def layer_backward(self, x, offset, offset_weight, weight, dy, want_dx=True, want_dow=True, want_dob=False,
+                       want_dw=True, want_dbias=False, x_channels_last: Optional[torch.Tensor] = None):
+        """Gradients of the layer: (dx, doffset_weight, doffset_bias, dweight, dbias); dx includes the path
+        through the offsets."""
+        x = self._act(x, "input")
+        weight = _prep(weight, "weight", x)
+        offset_weight = _prep(offset_weight, "offset_weight", x)
+        offset = _prep(offset, "offset", x)
+        self._check_offset(offset)
+        dy = self._act(dy, "grad_output", x)
+        dx = self._new_act(x.shape, x) if want_dx else None
+        dow = torch.empty_like(offset_weight) if want_dow else None
+        dob = torch.empty(self.offset_channels, dtype=x.dtype, device=x.device) if want_dob else None
+        dw = torch.empty(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
+        db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
+        ws, nb = self._layer_ws(_lib.PASS_BACKWARD)
+        with torch.cuda.device(x.device):
+            st = _lib.lib().dcn_layer_backward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset),
+                                               _lib.ptr(offset_weight), _lib.ptr(weight), _lib.ptr(dy),
+                                               _lib.ptr(x_channels_last), _lib.ptr(dx), _lib.ptr(dow), _lib.ptr(dob),
+                                               _lib.ptr(dw), _lib.ptr(db), _lib.ptr(ws), nb,
+                                               _lib.current_stream(x.device))
+        _lib.check(st, "dcn_layer_backward")
+        return dx, dow, dob, dw, db
+
     def debug_tc_points(self, offset: torch.Tensor, n: int):
         """Coordinates / validity / corner indices of sample ``n`` decoded from the sampling-point entries that the
         tensor-core backward-data kernel of the 2-D deformable operator consumes (bf16 precision)."""

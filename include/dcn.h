@@ -156,6 +156,40 @@ int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const 
                  const void* x_channels_last, void* dx, void* doffset, void* dweight, void* dbias, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Deformable layer: the caller pattern of the reference's model scripts in one call -- a plain
+ * convolution of x produces the offsets, the deformable convolution of the same x consumes them
+ * (deform3d/test_model.py:18-30, deform2d/test_model.py:19-31, where the two are separate modules
+ * and the offsets make a round trip through the framework's allocator).
+ * The offset-producing convolution is fixed by the deformable problem p: same input, taps, stride and
+ * padding, dilation 1 (the only one whose output size matches the deformable size rule), one group,
+ * dg*kv*D output channels, weight [dg*kv*D, C, k...], optional bias [dg*kv*D];
+ * dcn_offset_conv_problem fills q with it.  Offsets are always [N, dg*kv*D, out...], also with
+ * channels_last activations.
+ * With precision BF16 one channels-last bf16 copy of x serves both convolutions of the forward pass
+ * and all gradient kernels of the backward pass, and the offsets are read back while still in L2;
+ * with precision EXACT the calls below are the composition of the generic entry points.
+ * ------------------------------------------------------------------------------------------- */
+int dcn_offset_conv_problem(const dcn_problem* p, dcn_problem* q);
+
+/* Scratch bytes of dcn_layer_forward (pass = DCN_PASS_FORWARD) / dcn_layer_backward (DCN_PASS_BACKWARD). */
+size_t dcn_layer_workspace_bytes(const dcn_problem* p, int pass);
+
+/* offset = conv(x, offset_weight) + offset_bias;  y = deform_conv(x, offset, weight) + bias.
+ * `offset` (written) and `y` (written) are caller buffers; keep `offset` for the backward pass.
+ * BF16: the channels-last bf16 copy of x is left at the START of the workspace, as dcn_forward does. */
+int dcn_layer_forward(const dcn_problem* p, const void* x, const void* offset_weight, const void* offset_bias,
+                      const void* weight, const void* bias, void* offset, void* y, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* Gradients of the layer: dx (through the sampled values AND through the offsets), doffset_weight,
+ * doffset_bias, dweight, dbias; any may be NULL, every output is OVERWRITTEN.  The offset gradient itself
+ * lives in the workspace.  `x_channels_last` as in dcn_backward. */
+int dcn_layer_backward(const dcn_problem* p, const void* x, const void* offset, const void* offset_weight,
+                       const void* weight, const void* dy, const void* x_channels_last, void* dx,
+                       void* doffset_weight, void* doffset_bias, void* dweight, void* dbias, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 /* Debug aid for the bit-exactness tests: for sample `n` writes, for every (deformable group, tap,
  * output position), the sampling coordinate (tensor dtype, [dg,kv,ov,ndim]), validity (int32
  * [dg,kv,ov]) and the low / high corner index per axis (int32 [dg,kv,ov,ndim], -1 when invalid),

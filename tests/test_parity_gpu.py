@@ -83,6 +83,25 @@ def test_plain_conv2d_matches_torch():
         assert cases.rel_err(a.detach().cpu().numpy(), b_.detach().cpu().numpy()) <= 1e-5
 
 
+def test_plain_conv3d_matches_torch():
+    """The plain-convolution path over three spatial axes (conv2d/lib/conv2d_cuda.cpp:77-290 generalised): the
+    torch fp32 convolution is the reference for this floating-point kernel; fp32 gate 1e-5."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 6, 7, 9, 8, generator=g).cuda().requires_grad_(True)
+    m = dcn.Conv3d(6, 8, (3, 3, 2), stride=(1, 2, 1), padding=(1, 2, 0), dilation=(2, 1, 1), groups=2).cuda()
+    y = m(x)
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        ref = torch.nn.functional.conv3d(x, m.weight, m.bias, stride=(1, 2, 1), padding=(1, 2, 0), dilation=(2, 1, 1),
+                                         groups=2)
+        assert y.shape == ref.shape
+        dy = torch.randn_like(ref)
+        gx, gw, gb = torch.autograd.grad(ref, [x, m.weight, m.bias], dy)
+    hx, hw, hb = torch.autograd.grad(y, [x, m.weight, m.bias], dy)
+    for a, b_ in ((y, ref), (hx, gx), (hw, gw), (hb, gb)):
+        assert cases.rel_err(a.detach().cpu().numpy(), b_.detach().cpu().numpy()) <= 1e-5
+
+
 def test_fp64_gradcheck_like_the_reference():
     """deform2d_double/test_gradient.py:7-53 with torch's gradcheck (pull-back term off: it is not a derivative)."""
     import deform_conv3d_pytorch_op_b200 as dcn

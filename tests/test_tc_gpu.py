@@ -48,6 +48,26 @@ def test_bf16_plain_conv2d():
     assert cases.rel_err(hw.cpu().numpy(), gw.cpu().numpy()) <= TOL_BF16
 
 
+def test_bf16_plain_conv3d():
+    """Plain 3-D convolution on the tcgen05 kernels (DEFORM = false instantiations); bf16 gate 2e-2 against torch
+    fp32."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(2, 32, 6, 11, 9, generator=g).cuda().requires_grad_(True)
+    m = dcn.Conv3d(32, 40, 3, stride=(1, 2, 2), padding=1, dilation=1, groups=1, precision="bf16").cuda()
+    y = m(x)
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        ref = torch.nn.functional.conv3d(x, m.weight, m.bias, stride=(1, 2, 2), padding=1)
+        dy = torch.randn_like(ref)
+        gx, gw = torch.autograd.grad(ref, [x, m.weight], dy)
+    _check_status()
+    assert cases.rel_err(y.detach().cpu().numpy(), ref.detach().cpu().numpy()) <= TOL_BF16
+    hx, hw = torch.autograd.grad(y, [x, m.weight], dy)
+    _check_status()
+    assert cases.rel_err(hx.cpu().numpy(), gx.cpu().numpy()) <= TOL_BF16
+    assert cases.rel_err(hw.cpu().numpy(), gw.cpu().numpy()) <= TOL_BF16
+
+
 def test_bf16_is_deterministic_in_forward():
     case = cases.TC_CASES[0]
     tensors = cases.make_inputs(case)
