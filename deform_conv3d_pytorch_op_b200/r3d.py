@@ -15,17 +15,23 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+import os
+
+from .functions import DeformLayerFunction
 from .modules import ConvOffset3d
 
 
 class DeformUnit(nn.Module):
     """offset = conv3d(x) (same kernel / stride / padding, 3*27*dg channels, tiny init); y = deform_conv(x, offset).
     The reference's out-of-bounds pull-back term of the offset gradient is not a derivative of the loss; the model
-    trains with the true (zero) gradient for invalid samples unless ``oob_offset_grad=True``."""
+    trains with the true (zero) gradient for invalid samples unless ``oob_offset_grad=True``.
+    ``one_call`` (default: ``DCN_MODEL_ONE_CALL``, off): both convolutions through the library's layer entry point
+    instead of a stock convolution followed by the deformable operator; the parameters are the same either way."""
 
-    def __init__(self, cin, cout, stride, dg=4, precision="auto", deform=True, oob_offset_grad=False):
+    def __init__(self, cin, cout, stride, dg=4, precision="auto", deform=True, oob_offset_grad=False, one_call=None):
         super().__init__()
         self.deform = deform
+        self.one_call = (os.environ.get("DCN_MODEL_ONE_CALL", "0") not in ("", "0")) if one_call is None else one_call
         if deform:
             self.offset = nn.Conv3d(cin, dg * 27 * 3, 3, stride=stride, padding=1, bias=True)
             nn.init.normal_(self.offset.weight, std=0.01)
@@ -36,6 +42,11 @@ class DeformUnit(nn.Module):
             self.conv = nn.Conv3d(cin, cout, 3, stride=stride, padding=1, bias=False)
 
     def forward(self, x):
+        if self.deform and self.one_call:
+            c = self.conv
+            return DeformLayerFunction.apply(x, self.offset.weight, self.offset.bias, c.weight, c.bias, c.stride,
+                                             c.padding, c.dilation, c.channel_per_group, c.group, c.precision,
+                                             c.oob_offset_grad)
         if self.deform:
             return self.conv(x, self.offset(x))
         return self.conv(x)
