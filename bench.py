@@ -414,8 +414,10 @@ def run_small(args, wl):
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         keep = [one(i) for i in range(sets)]
-    # the launch floor: as many trivial nodes as a step has kernels and memsets (two kernels, three memsets)
-    tiny = [torch.zeros(1, device=dev) for _ in range(5)]
+    # the launch floor: as many trivial nodes as a step has kernels and zero fills (dX and dW are zero-filled before
+    # the backward kernel adds into them; with several convolution groups dOffset is too)
+    zero_fills = 2 + (1 if wl.G > 1 else 0)
+    tiny = [torch.zeros(1, device=dev) for _ in range(launches_per_step + zero_fills)]
     floor_graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(floor_graph):
         for _ in range(sets):
@@ -491,7 +493,7 @@ def run_small(args, wl):
     t_roof = max(wl.flops() / (peaks["bf16_tflops"] * 1e12), (fwd_b + bwd_b) / (peaks["hbm_gbs"] * 1e9))
     ach = (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9
     roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-            "traffic": None, "peak_source": peaks["source"], "kernel": "whole step (2 kernels + 3 memsets)",
+            "traffic": None, "peak_source": peaks["source"], "kernel": "whole step (%d kernels + %d zero fills)" % (launches_per_step, zero_fills),
             "t_roof_us": t_roof * 1e6, "launch_floor_us": floor_ms * 1e3,
             "frac_of_launch_floor": floor_ms / ms_per_step, "eager_step_us": eager_ms * 1e3,
             "note": "launch-latency bound: the roofline time is below one kernel launch; the floor is a CUDA graph of "

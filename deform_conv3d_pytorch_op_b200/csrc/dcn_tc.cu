@@ -447,8 +447,6 @@ int tc_backward_weight(const Geom& g, int ndim, int deform, const float* x, cons
     r = launch_pack_dy(g, dy, dpk, d.MT, d.PC, st);
     if (r != 0) return r;
     float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
-    r = dwpk_clear(g, dwpk, st);
-    if (r != 0) return r;
     if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dwpk, st)
                               : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dwpk, st);
     else r = deform ? launch_tc_wgrad<3, true>(g, xcl, off, dpk, dwpk, st)
@@ -519,8 +517,6 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
     }
     if (dw != nullptr) {
         float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
-        r = dwpk_clear(g, dwpk, st);
-        if (r != 0) return r;
         // the weight kernel reads dy tiles with the same layout and stride (PC2 == wg_dims().PC)
         if (ndim == 2) r = deform ? launch_tc_wgrad<2, true>(g, xcl, off, dpk, dwpk, st)
                                   : launch_tc_wgrad<2, false>(g, xcl, off, dpk, dwpk, st);
@@ -596,8 +592,6 @@ static int plain_backward_into(const Geom& gq, int ndim, bool dx_channels_last, 
     }
     if (dw_off != nullptr) {
         float* dwpk = reinterpret_cast<float*>(base + l.dwpk_off);
-        r = dwpk_clear(gq, dwpk, st);
-        if (r != 0) return r;
         r = ndim == 2 ? launch_tc_wgrad<2, false>(gq, xcl, nullptr, dpk, dwpk, st)
                       : launch_tc_wgrad<3, false>(gq, xcl, nullptr, dpk, dwpk, st);
         if (r != 0) return r;

@@ -14,6 +14,8 @@
 
 constexpr int kWgStages = 3;
 constexpr int kWgNMax = 256;
+// elements of one position split's slice of the packed dW scratch; `items` = G * MB * NB (the kernels' gridDim.x)
+__host__ __device__ inline size_t wg_slice_elems(unsigned items) { return (size_t)items * 256 * kWgNMax; }
 constexpr int kWgThreads = 32 * (2 + kProducerWarps + kEpilogueWarps);
 
 struct WgSmem {
@@ -213,8 +215,10 @@ tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, cons
             for (int mt = 0; mt < mtb; ++mt) {
                 const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
                 const bool o_ok = ol < g.Og;
-                // partial sums go to the packed scratch dwpk[G][MB*256 rows][NB*256 columns] as 16-byte reductions
-                float* dwo = dw + ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
+                // partial sums of this position split: plain stores into its slice of the packed scratch
+                // dwpk[split][G][MB*256 rows][NB*256 columns] (added up in split order by unpack_dw)
+                float* dwo = dw + (size_t)blockIdx.y * wg_slice_elems(gridDim.x) +
+                             ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
                 for (int cc = 0; cc < NW / 32; ++cc) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 32, v);
@@ -224,9 +228,9 @@ tc_wgrad_direct_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, cons
                     for (int i = 0; i < 8; ++i) {
                         const int kq = nb * kWgNMax + cc * 32 + 4 * i;
                         if (kq < g.kv * g.Cg)
-                            atomicAdd(reinterpret_cast<float4*>(dwo + cc * 32 + 4 * i),
-                                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+                            *reinterpret_cast<float4*>(dwo + cc * 32 + 4 * i) =
+                                make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                            __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
                     }
                 }
             }
@@ -265,11 +269,13 @@ inline WgDims wg_dims(const Geom& g) {
     return d;
 }
 
-// dwpk[G][rows][cols] (k' = tap * Cg + c along the columns) -> dW [O][Cg][kv] of the reference layout;
-// ACC adds to dW (the separate weight-gradient entry point accumulates), else dW is overwritten.
+// dwpk[split][G][rows][cols] (k' = tap * Cg + c along the columns) -> dW [O][Cg][kv] of the reference layout, the
+// position splits added in split order (deterministic); ACC adds to dW (the separate weight-gradient entry point
+// accumulates), else dW is overwritten.
 template <bool ACC>
 __global__ void __launch_bounds__(256)
-unpack_dw(const Geom g, const float* __restrict__ dwpk, float* __restrict__ dw, int rows, int cols) {
+unpack_dw(const Geom g, const float* __restrict__ dwpk, float* __restrict__ dw, int rows, int cols, int splits,
+          size_t slice) {
     const long long total = (long long)g.O * g.Cg * g.kv;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int tap = (int)(i % g.kv);
@@ -277,7 +283,17 @@ unpack_dw(const Geom g, const float* __restrict__ dwpk, float* __restrict__ dw, 
         const int c = (int)(oc % g.Cg);
         const int o = (int)(oc / g.Cg);
         const int j = o / g.Og, ol = o - j * g.Og;
-        const float v = dwpk[((size_t)j * rows + ol) * cols + (size_t)tap * g.Cg + c];
+        const float* src = dwpk + ((size_t)j * rows + ol) * cols + (size_t)tap * g.Cg + c;
+        // loads in batches of eight (independent, all in flight), additions in split order
+        float v = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = (s0 + u < splits) ? __ldg(src + (size_t)(s0 + u) * slice) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s0 + u < splits) v = (s0 + u == 0) ? t[u] : v + t[u];
+        }
         if (ACC) dw[i] += v;
         else dw[i] = v;
     }
@@ -285,19 +301,16 @@ unpack_dw(const Geom g, const float* __restrict__ dwpk, float* __restrict__ dw, 
 
 inline size_t dwpk_bytes(const Geom& g) {
     const WgDims d = wg_dims(g);
-    return (size_t)g.G * d.MB * 256 * d.NB * kWgNMax * sizeof(float);
+    return (size_t)d.splits * wg_slice_elems(g.G * d.MB * d.NB) * sizeof(float);
 }
 
-// Zero the packed scratch before the weight-gradient kernel, fold it into dW after it.
-inline int dwpk_clear(const Geom& g, float* dwpk, cudaStream_t st) {
-    return cudaMemsetAsync(dwpk, 0, dwpk_bytes(g), st) == cudaSuccess ? 0 : -5;
-}
 template <bool ACC>
 int dwpk_fold(const Geom& g, const float* dwpk, float* dw, cudaStream_t st) {
     const WgDims d = wg_dims(g);
     const long long total = (long long)g.O * g.Cg * g.kv;
-    const int blocks = (int)((total + 255) / 256 < 4 * sm_count() ? (total + 255) / 256 : 4 * sm_count());
-    unpack_dw<ACC><<<blocks, 256, 0, st>>>(g, dwpk, dw, d.MB * 256, d.NB * kWgNMax);
+    const int blocks = (int)((total + 255) / 256 < 16 * sm_count() ? (total + 255) / 256 : 16 * sm_count());
+    unpack_dw<ACC><<<blocks, 256, 0, st>>>(g, dwpk, dw, d.MB * 256, d.NB * kWgNMax, d.splits,
+                                           wg_slice_elems(g.G * d.MB * d.NB));
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

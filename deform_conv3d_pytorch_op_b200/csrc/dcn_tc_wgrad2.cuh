@@ -195,8 +195,12 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
             for (int mt = 0; mt < mtb; ++mt) {
                 const int ol = (mb * 2 + mt) * 128 + q * 32 + lane;
                 const bool o_ok = ol < g.Og;
-                // partial sums go to the packed scratch dwpk[G][MB*256 rows][NB*256 columns] as 16-byte reductions
-                float* dwo = dw + ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
+                // The partial sums of this position split go to ITS slice of the packed scratch
+                // dwpk[split][G][MB*256 rows][NB*256 columns] with plain 16-byte stores: every element a slice's
+                // reader touches is written exactly once, and unpack_dw adds the slices in split order, so dW does
+                // not depend on the order in which the CTAs finish.
+                float* dwo = dw + (size_t)blockIdx.y * wg_slice_elems(gridDim.x) +
+                             ((size_t)j * MB * 256 + (o_ok ? ol : 0)) * ((size_t)NB * kWgNMax) + (size_t)nb * kWgNMax;
                 for (int cc = 0; cc < NW / 16; ++cc) {
                     uint32_t v[16];
                     tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + mt * 256 + cc * 16, v);
@@ -206,9 +210,9 @@ tc_wgrad_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const float
                     for (int i = 0; i < 4; ++i) {
                         const int kq = nb * kWgNMax + cc * 16 + 4 * i;
                         if (kq < g.kv * g.Cg)
-                            atomicAdd(reinterpret_cast<float4*>(dwo + cc * 16 + 4 * i),
-                                      make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                  __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3])));
+                            *reinterpret_cast<float4*>(dwo + cc * 16 + 4 * i) =
+                                make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                            __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
                     }
                 }
             }

@@ -76,6 +76,18 @@ def test_bf16_is_deterministic_in_forward():
     assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("name", ["tc2_c256", "tc3_groups"])
+def test_bf16_weight_gradient_is_deterministic(name):
+    """The position splits of the weight gradient are stored in slices and added in split order (the reference
+    accumulates over the batch in a fixed order too: beta = 1 GEMMs in its sample loop,
+    deform3d/lib/deform_conv3d_cuda.cpp:278-330): two runs give the same bits."""
+    case = [c for c in cases.TC_CASES if c.name == name][0]
+    tensors = cases.make_inputs(case)
+    a = helpers.run_ours(case, tensors, "bf16")["dw"]
+    b = helpers.run_ours(case, tensors, "bf16")["dw"]
+    assert np.array_equal(a, b)
+
+
 @pytest.mark.parametrize("name", ["tc2_dg_groups", "tc3_groups", "tc2_c256"])
 def test_separate_bf16_passes_match_fused_backward(name):
     """dcn_backward_data / dcn_backward_weight (accumulate into zeroed buffers) against dcn_backward (overwrite,
