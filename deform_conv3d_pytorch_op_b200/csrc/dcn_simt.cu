@@ -12,6 +12,8 @@
 // P runs over the whole batch (N * out volume): the reference's serial per-sample loop is gone.
 #include "dcn_internal.h"
 
+#include <type_traits>
+
 namespace dcn {
 
 namespace {
@@ -52,11 +54,13 @@ __device__ __forceinline__ T sample_value(const Geom& g, const T* __restrict__ x
 // forward
 // grid.x: tiles of BN flattened positions; grid.y: G * ceil(Og / BM)
 // ---------------------------------------------------------------------------------------------
-template <typename T, int D, bool DEFORM>
+// BM output channels per CTA: every sampled element is gathered once per BM-row tile, and the gathers (scattered
+// 4-byte loads, one L1 tag look-up each) are what bounds this kernel, so wide problems take 256-row tiles.
+template <typename T, int D, bool DEFORM, int BM>
 __global__ void __launch_bounds__(kThreads)
 simt_forward_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off, const T* __restrict__ w,
                     const T* __restrict__ bias, T* __restrict__ y) {
-    constexpr int BM = 128, BN = 64, BK = 16, TM = 8, TN = 4;
+    constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
     __shared__ T As[BK][BM + 4];
     __shared__ T Bs[BK][BN + 4];
 
@@ -352,11 +356,11 @@ simt_backward_data_kernel(const Geom g, const T* __restrict__ x, const T* __rest
 // backward weight: dW[o, k] += sum_P dy[o, P] * sample(k, P);  grid.z splits the position range
 // grid.x: ceil(Kg / BN) ; grid.y: G * ceil(Og / BM)
 // ---------------------------------------------------------------------------------------------
-template <typename T, int D, bool DEFORM>
+template <typename T, int D, bool DEFORM, int BM = 64>
 __device__ __forceinline__ void
 simt_backward_weight_body(const uint3 bid, const Geom g, const T* __restrict__ x, const T* __restrict__ off,
                             const T* __restrict__ dy, T* __restrict__ dw, int chunks_per_split) {
-    constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+    constexpr int BN = 64, BK = 16, TM = BM / 16, TN = 4;
     __shared__ T As[BK][BM + 4];
     __shared__ T Bs[BK][BN + 4];
 
@@ -430,11 +434,12 @@ simt_backward_weight_body(const uint3 bid, const Geom g, const T* __restrict__ x
 }
 
 // dbias[o] = sum over n and positions of dy  (deform3d/deform_conv3d_functions/deform_conv3d_function.py:73-74)
-template <typename T, int D, bool DEFORM>
+// (BM: as in the forward kernel, the sampled elements of a position chunk serve BM output channels)
+template <typename T, int D, bool DEFORM, int BM>
 __global__ void __launch_bounds__(kThreads)
 simt_backward_weight_kernel(const Geom g, const T* __restrict__ x, const T* __restrict__ off,
                             const T* __restrict__ dy, T* __restrict__ dw, int chunks_per_split) {
-    simt_backward_weight_body<T, D, DEFORM>(blockIdx, g, x, off, dy, dw, chunks_per_split);
+    simt_backward_weight_body<T, D, DEFORM, BM>(blockIdx, g, x, off, dy, dw, chunks_per_split);
 }
 
 // Both backward passes in one launch, for problems so small that the launch itself is what they cost: the first
@@ -519,9 +524,17 @@ __global__ void debug_points_kernel(const Geom g, const T* __restrict__ off, int
 template <typename T, int D, bool DEFORM>
 int launch_forward(const Geom& g, const void* x, const void* off, const void* w, const void* bias, void* y,
                    cudaStream_t st) {
+    if constexpr (std::is_same<T, float>::value) {
+        if (g.Og > 128) {
+            dim3 grid((unsigned)((g.P + 63) / 64), (unsigned)(g.G * ((g.Og + 255) / 256)));
+            simt_forward_kernel<T, D, DEFORM, 256><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off, (const T*)w,
+                                                                              (const T*)bias, (T*)y);
+            return cudaGetLastError() == cudaSuccess ? 0 : -5;
+        }
+    }
     dim3 grid((unsigned)((g.P + 63) / 64), (unsigned)(g.G * ((g.Og + 127) / 128)));
-    simt_forward_kernel<T, D, DEFORM><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off, (const T*)w,
-                                                                 (const T*)bias, (T*)y);
+    simt_forward_kernel<T, D, DEFORM, 128><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off, (const T*)w,
+                                                                      (const T*)bias, (T*)y);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -539,9 +552,9 @@ int launch_backward_data(const Geom& g, const void* x, const void* off, const vo
 }
 
 // Work split of the weight pass: (grid, position chunks per split).
-inline void weight_grid(const Geom& g, dim3& grid, int& cps) {
+inline void weight_grid(const Geom& g, dim3& grid, int& cps, int bm = 64) {
     const long long chunks = (g.P + 15) / 16;
-    const long long tiles = (long long)((g.Kg + 63) / 64) * g.G * ((g.Og + 63) / 64);
+    const long long tiles = (long long)((g.Kg + 63) / 64) * g.G * ((g.Og + bm - 1) / bm);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms < 1) sms = 148;
@@ -551,7 +564,7 @@ inline void weight_grid(const Geom& g, dim3& grid, int& cps) {
     if (splits > 65535) splits = 65535;
     cps = (int)((chunks + splits - 1) / splits);
     splits = (chunks + cps - 1) / cps;
-    grid = dim3((unsigned)((g.Kg + 63) / 64), (unsigned)(g.G * ((g.Og + 63) / 64)), (unsigned)splits);
+    grid = dim3((unsigned)((g.Kg + 63) / 64), (unsigned)(g.G * ((g.Og + bm - 1) / bm)), (unsigned)splits);
 }
 
 template <typename T, int D, bool DEFORM>
@@ -559,9 +572,22 @@ int launch_backward_weight(const Geom& g, const void* x, const void* off, const 
                            cudaStream_t st) {
     dim3 grid;
     int cps;
+    if constexpr (std::is_same<T, float>::value) {
+        if (g.Og > 64) {
+            const int bm = g.Og > 128 ? 256 : 128;
+            weight_grid(g, grid, cps, bm);
+            if (bm == 256)
+                simt_backward_weight_kernel<T, D, DEFORM, 256><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off,
+                                                                                         (const T*)dy, (T*)dw, cps);
+            else
+                simt_backward_weight_kernel<T, D, DEFORM, 128><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off,
+                                                                                         (const T*)dy, (T*)dw, cps);
+            return cudaGetLastError() == cudaSuccess ? 0 : -5;
+        }
+    }
     weight_grid(g, grid, cps);
-    simt_backward_weight_kernel<T, D, DEFORM><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off,
-                                                                         (const T*)dy, (T*)dw, cps);
+    simt_backward_weight_kernel<T, D, DEFORM, 64><<<grid, kThreads, 0, st>>>(g, (const T*)x, (const T*)off,
+                                                                             (const T*)dy, (T*)dw, cps);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
