@@ -161,7 +161,11 @@ template <int D, bool DEFORM>
 __device__ __forceinline__ uint4 gather_finish_w(const uint4 (&q)[DEFORM ? (1 << D) : 1],
                                                  const float (&w)[DEFORM ? (1 << D) : 1]) {
     if constexpr (!DEFORM) return q[0];
-#ifdef DCN_INTERP_BF16X2
+#ifndef DCN_INTERP_FP32
+    // Packed bf16 arithmetic: 16 two-wide FMAs per 8 channels and no unpacking, against 16 two-wide fp32 FMAs plus
+    // 32 unpack and pack operations (build with -DDCN_INTERP_FP32 for the fp32 form).  The sampled value is rounded
+    // to bf16 for the MMA either way; rounding the partial sums too raises the measured error of y / dW at the
+    // tensor-core test shapes from 3.3e-3 to 4.6e-3 of max|ref| (gate 2e-2) and takes 7-8 % off both kernels.
     else {
         uint32_t acc[4];
 #pragma unroll
