@@ -79,6 +79,24 @@ def test_null_pointers_are_refused_before_any_launch(L):
     assert L.dcn_backward_weight(ctypes.byref(ok), None, None, None, None, None, None, 0, None) == -1
 
 
+def test_offset_conv_problem_of_a_layer(L):
+    """The convolution that produces a deformable problem's offsets (caller pattern deform3d/test_model.py:18-30):
+    same taps, stride, padding, dilation 1, dg*kv*D output channels, and the deformable problem's output size."""
+    p = _lib.make_problem(3, torch.float32, 2, 8, 6, (5, 9, 9), (3, 3, 3), (1, 2, 2), (1, 2, 2), (2, 2, 2), 2, 4)
+    q = _lib.dcn_problem()
+    assert L.dcn_offset_conv_problem(ctypes.byref(p), ctypes.byref(q)) == 0
+    assert (q.O, q.G, q.deformable, q.C, q.N) == (2 * 27 * 3, 1, 0, 8, 2)
+    assert tuple(q.dil) == (1, 1, 1) and tuple(q.k) == tuple(p.k) and tuple(q.stride) == tuple(p.stride)
+    assert _lib.output_size(q) == _lib.output_size(p)
+    plain = _p(deformable=False, std_size_rule=True)
+    assert L.dcn_offset_conv_problem(ctypes.byref(plain), ctypes.byref(q)) == -3      # not a deformable problem
+    # EXACT precision: the layer's backward workspace is the offset gradient, the forward needs none
+    n_off = 2 * (2 * 27 * 3) * int(torch.Size(_lib.output_size(p)).numel()) * 4
+    assert L.dcn_layer_workspace_bytes(ctypes.byref(p), _lib.PASS_FORWARD) == 0
+    assert n_off <= L.dcn_layer_workspace_bytes(ctypes.byref(p), _lib.PASS_BACKWARD) < n_off + 256
+    assert L.dcn_layer_forward(ctypes.byref(p), None, None, None, None, None, None, None, None, 0, None) == -1
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdcn.so")
@@ -100,3 +118,8 @@ def test_module_surface():
     assert leg.bias is None and leg.dilation == (1, 1)
     c = dcn.Conv2d(4, 6, 3, groups=2)
     assert tuple(c.weight.shape) == (6, 2, 3, 3)
+    c3 = dcn.Conv3d(4, 6, (1, 3, 3), groups=2)
+    assert tuple(c3.weight.shape) == (6, 2, 1, 3, 3)
+    layer = dcn.DeformLayer3d(8, 16, 3, padding=1, deformable_groups=2)
+    assert tuple(layer.conv_offset.weight.shape) == (2 * 27 * 3, 8, 3, 3, 3)
+    assert set(layer.state_dict().keys()) == {"conv.weight", "conv.bias", "conv_offset.weight", "conv_offset.bias"}
