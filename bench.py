@@ -414,9 +414,8 @@ def run_small(args, wl):
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         keep = [one(i) for i in range(sets)]
-    # the launch floor: as many trivial nodes as a step has kernels and zero fills (dX and dW are zero-filled before
-    # the backward kernel adds into them; with several convolution groups dOffset is too)
-    zero_fills = 2 + (1 if wl.G > 1 else 0)
+    # the launch floor: as many trivial nodes as a step has kernels and zero fills
+    zero_fills = 0 if prec == "exact" else 2            # the exact small-problem path zero-fills in a kernel of its own
     tiny = [torch.zeros(1, device=dev) for _ in range(launches_per_step + zero_fills)]
     floor_graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(floor_graph):

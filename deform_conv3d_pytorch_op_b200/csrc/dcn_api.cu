@@ -132,9 +132,11 @@ int dcn_launch_count(const dcn_problem* p, int pass) {
     if (validate(p) != DCN_OK) return 0;
     Geom g;
     make_geom(p, g);
-    if (p->precision == DCN_PREC_EXACT)
-        return (pass == DCN_PASS_BACKWARD && !dcn::simt_backward_both_supported(g, p->dtype) &&
-                !dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable)) ? 2 : 1;
+    if (p->precision == DCN_PREC_EXACT) {
+        if (pass != DCN_PASS_BACKWARD) return 1;
+        if (dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable)) return 2;      // zero fill + one kernel
+        return dcn::simt_backward_both_supported(g, p->dtype) ? 1 : 2;
+    }
     if (!dcn::tc_supported(g, p->ndim, p->deformable)) return 0;
     return dcn::tc_launch_count(g, p->ndim, p->deformable, pass);
 }
@@ -253,12 +255,15 @@ int dcn_backward(const dcn_problem* p, const void* x, const void* offset, const 
                                  ws_bytes, st);
         } else {
             const size_t es = p->dtype == DCN_F64 ? 8 : 4;
-            if (dx != nullptr && cudaMemsetAsync(dx, 0, (size_t)g.N * g.C * g.iv * es, st) != cudaSuccess) return DCN_ERR_CUDA;
-            if (dweight != nullptr && cudaMemsetAsync(dweight, 0, (size_t)g.O * g.Cg * g.kv * es, st) != cudaSuccess)
+            const bool small = dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable);
+            // (the small-problem path zero-fills its outputs itself, in one launch that its main kernel overlaps)
+            if (!small && dx != nullptr && cudaMemsetAsync(dx, 0, (size_t)g.N * g.C * g.iv * es, st) != cudaSuccess)
+                return DCN_ERR_CUDA;
+            if (!small && dweight != nullptr && cudaMemsetAsync(dweight, 0, (size_t)g.O * g.Cg * g.kv * es, st) != cudaSuccess)
                 return DCN_ERR_CUDA;
             const bool all = dx != nullptr && dweight != nullptr && (!p->deformable || doffset != nullptr);
-            if (dcn::simt_small_supported(g, p->dtype, p->ndim, p->deformable)) {
-                r = dcn::simt_small_backward(g, p->ndim, x, offset, weight, dy, dx, doffset, dweight, st);   // one launch
+            if (small) {
+                r = dcn::simt_small_backward(g, p->ndim, x, offset, weight, dy, dx, doffset, dweight, st);
             } else if (all && dcn::simt_backward_both_supported(g, p->dtype)) {
                 r = dcn::simt_backward_both(g, p->ndim, p->deformable, x, offset, weight, dy, dx,
                                             p->deformable ? doffset : nullptr, dweight, st);     // one launch

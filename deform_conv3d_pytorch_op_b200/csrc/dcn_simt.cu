@@ -12,6 +12,7 @@
 // P runs over the whole batch (N * out volume): the reference's serial per-sample loop is gone.
 #include "dcn_internal.h"
 
+#include <stdlib.h>
 #include <type_traits>
 
 namespace dcn {

@@ -148,8 +148,9 @@ small_forward_kernel(const Geom g, const float* __restrict__ x, const float* __r
     }
 }
 
-// dx and dw must be zero-filled by the caller; doff is written with plain stores when DOFF_PLAIN (one conv group:
-// a CTA then holds every channel of the deformable groups it touches), else added to a zero-filled doff.
+// dx and dw must be zero-filled by the launch before this one (see launch_small_backward); doff is written with
+// plain stores when DOFF_PLAIN (one conv group: a CTA then holds every channel of the deformable groups it touches),
+// else added to a zero-filled doff.
 template <int D, bool DOFF_PLAIN>
 __global__ void __launch_bounds__(kSmallThreads)
 small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __restrict__ off,
@@ -180,6 +181,9 @@ small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __
     for (int i = threadIdx.x; i < TP * g.kv * ndg * D; i += kSmallThreads) dacc[i] = 0.f;
     small_points<D>(g, off, j, TP, ndg, P0, pts);
     __syncthreads();
+    // Everything above only reads inputs.  The outputs are zero-filled by the launch before this one, which this
+    // kernel may overlap (programmatic dependent launch): wait for it here, before the first addition.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 #pragma unroll 2
     for (int it = threadIdx.x; it < TP * g.Kg; it += kSmallThreads) {
         const int pl = it % TP, k = it / TP;
@@ -278,23 +282,67 @@ int launch_small_forward(const Geom& g, const float* x, const float* off, const 
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+// Zero fill of up to three output buffers in one launch; lets the dependent launch start at once.
+__global__ void __launch_bounds__(256)
+small_zero_kernel(float4* __restrict__ a, size_t na4, float4* __restrict__ b, size_t nb4, float4* __restrict__ c, size_t nc4) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < na4; i += stride) a[i] = z;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nb4; i += stride) b[i] = z;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nc4; i += stride) c[i] = z;
+}
+
+inline bool small_pdl_enabled() {
+    static const bool off = [] { const char* e = getenv("DCN_PDL"); return e != nullptr && e[0] == '0'; }();
+    return !off;
+}
+
+// dX, dW (and dOffset with several convolution groups) are zero-filled here: by one kernel when the buffers allow
+// 16-byte stores, and then the main kernel is launched as its programmatic dependent, so that its input-only
+// prologue (weights, dy tile, sampling points) runs while the zero fill is still in flight.
 template <int D>
 int launch_small_backward(const Geom& g, const float* x, const float* off, const float* w, const float* dy, float* dx,
                           float* doff, float* dw, cudaStream_t st) {
     const SmallDims d = small_dims(g, D);
     dim3 grid((unsigned)((g.P + d.TP - 1) / d.TP), (unsigned)g.G);
+    const size_t ndx = dx != nullptr ? (size_t)g.N * g.C * g.iv : 0;
+    const size_t ndw = dw != nullptr ? (size_t)g.O * g.Cg * g.kv : 0;
+    const size_t ndo = (g.G > 1 && doff != nullptr) ? (size_t)g.N * g.dg * g.kv * D * g.ov : 0;
+    auto vec_ok = [](const void* p, size_t n) { return n % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    bool pdl = small_pdl_enabled() && vec_ok(dx, ndx) && vec_ok(dw, ndw) && vec_ok(doff, ndo);
+    if (pdl) {
+        const size_t most = (ndx > ndw ? ndx : ndw) / 4;
+        const int blocks = (int)((most + 255) / 256 < 296 ? ((most + 255) / 256 > 0 ? (most + 255) / 256 : 1) : 296);
+        small_zero_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<float4*>(dx), ndx / 4, reinterpret_cast<float4*>(dw),
+                                                  ndw / 4, reinterpret_cast<float4*>(doff), ndo / 4);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+    } else {
+        if (ndx != 0 && cudaMemsetAsync(dx, 0, ndx * sizeof(float), st) != cudaSuccess) return -5;
+        if (ndw != 0 && cudaMemsetAsync(dw, 0, ndw * sizeof(float), st) != cudaSuccess) return -5;
+        if (ndo != 0 && cudaMemsetAsync(doff, 0, ndo * sizeof(float), st) != cudaSuccess) return -5;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kSmallThreads);
+    cfg.dynamicSmemBytes = (size_t)d.smem_bwd;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
     if (g.G == 1) {
         auto kern = small_backward_kernel<D, true>;
         if (d.smem_bwd > 48 * 1024 &&
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
-        kern<<<grid, kSmallThreads, d.smem_bwd, st>>>(g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
+        e = cudaLaunchKernelEx(&cfg, kern, g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
     } else {
-        if (doff != nullptr &&
-            cudaMemsetAsync(doff, 0, (size_t)g.N * g.dg * g.kv * D * g.ov * sizeof(float), st) != cudaSuccess) return -5;
         auto kern = small_backward_kernel<D, false>;
         if (d.smem_bwd > 48 * 1024 &&
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
-        kern<<<grid, kSmallThreads, d.smem_bwd, st>>>(g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
+        e = cudaLaunchKernelEx(&cfg, kern, g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
     }
-    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+    return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -5;
 }
