@@ -93,8 +93,10 @@ def test_layer_bf16_against_separate_calls_and_fp32(ndim, channels_last):
                  precision="bf16")
     dx_q, _, dow2, dob2 = opq.backward(xs, None, m.conv_offset.weight, doff, True, False, True, True)
     assert _rel(dw, dw2) <= 1e-5 and _rel(db, db2) <= 1e-5
-    assert _rel(dow, dow2) <= 1e-4 and _rel(dob, dob2) <= 1e-4
-    assert _rel(dx, dx_m + dx_q) <= 1e-4
+    # (gates downstream of dOffset are wider: its last bits depend on the order of the slabs' atomics, and a value on a
+    # bf16 rounding boundary moves the packed operand of the plain convolution's gradient kernels by one bf16 step)
+    assert _rel(dow, dow2) <= 1e-3 and _rel(dob, dob2) <= 1e-4
+    assert _rel(dx, dx_m + dx_q) <= 1e-3
     # (b) against fp32 arithmetic
     with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
         off_ref = _stock_conv(ndim)(xs, m.conv_offset.weight, m.conv_offset.bias, stride=c.stride, padding=c.padding)
@@ -121,3 +123,32 @@ def test_layer_rejects_wrong_offset_weight_shape():
     op = dcn.Op(x, c.weight, c.stride, c.padding, c.dilation, c.channel_per_group, c.group)
     with pytest.raises(dcn.DcnError):
         op.layer_forward(x, m.conv_offset.weight[:, :4].contiguous(), None, c.weight, None)
+
+
+def test_layer_at_benchmark_shape_matches_separate_calls():
+    """Config-2 shape (256 -> 256 channels, 56 x 56, 4 deformable groups) at batch 4, bf16 path: the shared-memory
+    backward-data kernel and the table-driven forward / weight kernels inside the layer call give what the separate
+    calls give; offsets against the fp32 convolution within the bf16 gate."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    m, x = _make(2, 4, 256, 256, (56, 56), 3, 1, 1, 1, 4, 1, seed=9, offset_std=0.02)
+    c = m.conv
+    op = dcn.Op(x, c.weight, c.stride, c.padding, c.dilation, c.channel_per_group, c.group, precision="bf16")
+    y, off, ws = op.layer_forward(x, m.conv_offset.weight, m.conv_offset.bias, c.weight, c.bias, keep_workspace=True)
+    dy = torch.randn_like(y)
+    dx, dow, dob, dw, db = op.layer_backward(x, off, m.conv_offset.weight, c.weight, dy, True, True, True, True, True, ws)
+    dcn.check_status()
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        off_ref = torch.nn.functional.conv2d(x, m.conv_offset.weight, m.conv_offset.bias, stride=c.stride, padding=c.padding)
+    assert _rel(off, off_ref) <= TOL_BF16
+    assert _rel(y, op.forward(x, off, c.weight, c.bias)) <= 1e-6
+    dx_m, doff, dw2, db2 = op.backward(x, off, c.weight, dy, True, True, True, True)
+    opq = dcn.Op(x, m.conv_offset.weight, c.stride, c.padding, 1, x.size(1), 1, deformable=False, std_size_rule=True,
+                 precision="bf16")
+    dx_q, _, dow2, dob2 = opq.backward(x, None, m.conv_offset.weight, doff, True, False, True, True)
+    assert torch.equal(dw, dw2)                      # ordered split-K: bit for bit
+    # dOffset is summed over the 8 channel slabs of a deformable group with floating-point atomics, so two runs differ
+    # in its last bits; where such a value sits on a bf16 rounding boundary the packed operand of the plain
+    # convolution's gradient kernels moves by one bf16 step (4e-3 of the term), hence the wider gates downstream of it
+    assert _rel(db, db2) <= 1e-5 and _rel(dob, dob2) <= 1e-4
+    assert _rel(dow, dow2) <= 1e-3
+    assert _rel(dx, dx_m + dx_q) <= 1e-3
