@@ -1,0 +1,86 @@
+"""Seeded random geometries through both CUDA paths against the CPU oracle.
+
+The reference tests a handful of hand-picked recipes (deform3d/test_gradient.py:9-30, deform2d_double/
+test_gradient.py:7-53); the fixed cases of tests/cases.py restate them and add corners.  This sweep draws
+geometries at random (dimensionality, groups, deformable groups, rectangular kernels, stride, padding, dilation,
+ragged sizes, offsets large enough to leave the input) so that index arithmetic nobody thought to write a case for
+gets exercised too.  Gates: exact path 1e-4 against the fp32 oracle (same arithmetic), bf16 path 2e-2 against the
+float64 oracle evaluated at the reference's fp32 coordinates."""
+import numpy as np
+import pytest
+
+from tests import cases, helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def _draw(rng, ndim, tensor_core):
+    for _ in range(200):
+        G = int(rng.choice([1, 1, 2, 4])) if not tensor_core else int(rng.choice([1, 1, 2]))
+        if tensor_core:
+            cpg = int(rng.choice([8, 16]))
+            cg = cpg * int(rng.choice([1, 2]))              # channels per convolution group: whole deformable groups
+            og = int(rng.choice([8, 16, 24, 40]))
+        else:
+            cpg = int(rng.choice([1, 2, 3, 4]))
+            cg = cpg * int(rng.choice([1, 2, 3]))
+            og = int(rng.integers(1, 6))
+        C, O = G * cg, G * og
+        if C % cpg != 0:
+            continue
+        k = tuple(int(v) for v in rng.integers(1, 4, ndim))
+        stride = tuple(int(v) for v in rng.integers(1, 3, ndim))
+        pad = tuple(int(v) for v in rng.integers(0, 3, ndim))
+        dil = tuple(int(v) for v in rng.integers(1, 3, ndim))
+        lo, hi = (3, 8) if ndim == 3 else (4, 14)
+        size = tuple(int(v) for v in rng.integers(lo, hi, ndim))
+        if any((s + 2 * p - kk) // st + 1 < 1 or s + 2 * p < kk for s, p, kk, st in zip(size, pad, k, stride)):
+            continue
+        return dict(ndim=ndim, N=int(rng.integers(1, 4)), C=C, O=O, in_size=size, kernel=k, stride=stride, pad=pad,
+                    dil=dil, G=G, cpg=cpg, bias=bool(rng.integers(0, 2)), offset_std=float(rng.choice([0.5, 1.5, 3.0])))
+    raise RuntimeError("no valid geometry drawn")
+
+
+def _cases(seed, count, tensor_core, dtype="float32"):
+    rng = np.random.default_rng(seed)
+    out = []
+    for i in range(count):
+        kw = _draw(rng, 2 + (i % 2), tensor_core)
+        tag = "_tc" if tensor_core else ("_f64" if dtype == "float64" else "")
+        out.append(cases.Case("rnd%s_%d" % (tag, i), dtype=dtype, **kw))
+    return out
+
+
+# fp32: these sizes take the latency-shaped small-problem kernels; fp64: the tiled kernels
+@pytest.mark.parametrize("case", _cases(20240607, 24, False) + _cases(31337, 12, False, "float64"), ids=lambda c: c.name)
+def test_exact_path_on_random_geometries(case):
+    tensors = cases.make_inputs(case)
+    ours = helpers.run_ours(case, tensors, "exact")
+    same = helpers.run_oracle(case, tensors)
+    tol = 1e-4 if case.dtype == "float32" else 1e-10
+    for k in same:
+        assert ours[k].shape == same[k].shape, (k, case)
+        assert cases.rel_err(ours[k], same[k]) <= tol, (k, cases.rel_err(ours[k], same[k]), case)
+
+
+@pytest.mark.parametrize("case", _cases(977, 16, True), ids=lambda c: c.name)
+def test_bf16_path_on_random_geometries(case):
+    import deform_conv3d_pytorch_op_b200 as dcn
+    tensors = list(cases.make_inputs(case))
+    off32 = helpers.offsets_at_fp32_coordinates(case, tensors[2].numpy())
+    ours = helpers.run_ours(case, tensors, "bf16")
+    dcn.check_status()
+    t64 = [None if t is None else t.numpy().astype(np.float64) for t in tensors]
+    x, w, _, dy, b = t64
+    p = case.problem()
+    p.N = x.shape[0]
+    from oracle import oracle as orc
+    ref = {"y": orc.forward(p, x, off32, w, b)}
+    ref["dx"], ref["doff"] = orc.backward_data(p, x, off32, w, dy)
+    ref["dw"] = orc.backward_weight(p, x, off32, dy)
+    mask = helpers.lattice_mask(case, tensors[2].numpy())
+    for k in ("y", "dx", "dw", "doff"):
+        a, r = ours[k].astype(np.float64), ref[k]
+        if k == "doff":
+            a, r = np.where(mask, 0, a), np.where(mask, 0, r)
+        assert cases.rel_err(a, r) <= 2e-2, (k, cases.rel_err(a, r), case)
