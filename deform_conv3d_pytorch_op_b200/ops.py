@@ -45,6 +45,28 @@ def status_check_enabled() -> bool:
     return os.environ.get("DCN_CHECK_STATUS", "0") not in ("", "0")
 
 
+def _nvtx_enabled() -> bool:
+    """``DCN_NVTX=1``: wrap every library call of :class:`Op` in an NVTX range named after the entry point, so that
+    the passes show up by name on a profiler's timeline (the reference has only wall-clock prints,
+    deform2d/test_function.py:30-58)."""
+    return os.environ.get("DCN_NVTX", "0") not in ("", "0")
+
+
+class _Range:
+    def __init__(self, name: str):
+        self.on = _nvtx_enabled()
+        self.name = name
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def _prep(t: Optional[torch.Tensor], name: str, ref: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     if t is None:
         return None
@@ -161,7 +183,7 @@ class Op:
         dw = torch.empty(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
         db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
         ws, nb = self._ws(_lib.PASS_BACKWARD)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Range("dcn_backward"):
             st = _lib.lib().dcn_backward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
                                          _lib.ptr(dy), _lib.ptr(x_channels_last), _lib.ptr(dx), _lib.ptr(doff),
                                          _lib.ptr(dw), _lib.ptr(db), _lib.ptr(ws), nb, _lib.current_stream(x.device))
@@ -179,7 +201,7 @@ class Op:
             offset = None
         y = self._new_act((self.N, self.O) + tuple(self.out_size), x)
         ws, nb = self._ws(_lib.PASS_FORWARD)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Range("dcn_forward"):
             st = _lib.lib().dcn_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(weight),
                                         _lib.ptr(bias), _lib.ptr(y), _lib.ptr(ws), nb, _lib.current_stream(x.device))
         _lib.check(st, "dcn_forward")
@@ -207,7 +229,7 @@ class Op:
         if dx is None and doff is None:
             return None, None
         ws, nb = self._ws(_lib.PASS_BACKWARD_DATA)
-        with torch.cuda.device(dy.device):
+        with torch.cuda.device(dy.device), _Range("dcn_backward_data"):
             st = _lib.lib().dcn_backward_data(ctypes.byref(self.p), _lib.ptr(x) if self.deformable else None,
                                               _lib.ptr(offset), _lib.ptr(weight), _lib.ptr(dy), _lib.ptr(dx),
                                               _lib.ptr(doff), _lib.ptr(ws), nb, _lib.current_stream(dy.device))
@@ -224,7 +246,7 @@ class Op:
         if dw is None and db is None:
             return None, None
         ws, nb = self._ws(_lib.PASS_BACKWARD_WEIGHT) if want_dw else (None, 0)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Range("dcn_backward_weight"):
             st = _lib.lib().dcn_backward_weight(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset), _lib.ptr(dy),
                                                 _lib.ptr(dw), _lib.ptr(db), _lib.ptr(ws), nb,
                                                 _lib.current_stream(x.device))
@@ -258,7 +280,7 @@ class Op:
         y = self._new_act((self.N, self.O) + tuple(self.out_size), x)
         offset = torch.empty((self.N, self.offset_channels) + tuple(self.out_size), dtype=x.dtype, device=x.device)
         ws, nb = self._layer_ws(_lib.PASS_FORWARD)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Range("dcn_layer_forward"):
             st = _lib.lib().dcn_layer_forward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset_weight),
                                               _lib.ptr(offset_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(offset),
                                               _lib.ptr(y), _lib.ptr(ws), nb, _lib.current_stream(x.device))
@@ -281,7 +303,7 @@ class Op:
         dw = torch.empty(self.weight_shape, dtype=x.dtype, device=x.device) if want_dw else None
         db = torch.empty(self.O, dtype=x.dtype, device=x.device) if want_dbias else None
         ws, nb = self._layer_ws(_lib.PASS_BACKWARD)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Range("dcn_layer_backward"):
             st = _lib.lib().dcn_layer_backward(ctypes.byref(self.p), _lib.ptr(x), _lib.ptr(offset),
                                                _lib.ptr(offset_weight), _lib.ptr(weight), _lib.ptr(dy),
                                                _lib.ptr(x_channels_last), _lib.ptr(dx), _lib.ptr(dow), _lib.ptr(dob),
@@ -302,7 +324,7 @@ class Op:
         lo = torch.empty((dg, kv, ov, self.ndim), dtype=torch.int32, device=offset.device)
         hi = torch.empty_like(lo)
         ws, nb = self._ws(_lib.PASS_BACKWARD)
-        with torch.cuda.device(offset.device):
+        with torch.cuda.device(offset.device), _Range("dcn_debug_tc_points"):
             st = _lib.lib().dcn_debug_tc_points(ctypes.byref(self.p), _lib.ptr(offset), n, _lib.ptr(coords),
                                                 _lib.ptr(valid), _lib.ptr(lo), _lib.ptr(hi), _lib.ptr(ws), nb,
                                                 _lib.current_stream(offset.device))
@@ -319,7 +341,7 @@ class Op:
         valid = torch.empty((dg, kv, ov), dtype=torch.int32, device=offset.device)
         lo = torch.empty((dg, kv, ov, self.ndim), dtype=torch.int32, device=offset.device)
         hi = torch.empty_like(lo)
-        with torch.cuda.device(offset.device):
+        with torch.cuda.device(offset.device), _Range("dcn_debug_points"):
             st = _lib.lib().dcn_debug_points(ctypes.byref(self.p), _lib.ptr(offset), n, _lib.ptr(coords),
                                              _lib.ptr(valid), _lib.ptr(lo), _lib.ptr(hi),
                                              _lib.current_stream(offset.device))
