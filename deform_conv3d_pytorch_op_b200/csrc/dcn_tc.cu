@@ -93,9 +93,9 @@ weight_to_kmajor_bf16(const Geom g, const float* __restrict__ w, __nv_bfloat16* 
     const float* src = w + (size_t)o * g.Cg * g.kv;
     __nv_bfloat16* dst = wt + (size_t)o * g.Kg;
     float mx = 0.f;
-    for (int c0 = 0; c0 < g.Cg; c0 += kWtChunk) {
+    {
+        const int c0 = blockIdx.y * kWtChunk;                        // one piece of 64 channels per block
         const int nc = g.Cg - c0 < kWtChunk ? g.Cg - c0 : kWtChunk;
-        __syncthreads();
         for (int i = threadIdx.x; i < nc * g.kv; i += blockDim.x) {
             const float v = __ldg(src + (size_t)c0 * g.kv + i);
             wrow[i] = v;
@@ -123,7 +123,7 @@ int launch_weight_to_kmajor(const Geom& g, const float* w, __nv_bfloat16* wt, un
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(weight_to_kmajor_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return -5;
-    weight_to_kmajor_bf16<<<g.O, 256, smem, st>>>(g, w, wt, wmax_bits);
+    weight_to_kmajor_bf16<<<dim3((unsigned)g.O, (unsigned)((g.Cg + kWtChunk - 1) / kWtChunk)), 256, smem, st>>>(g, w, wt, wmax_bits);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

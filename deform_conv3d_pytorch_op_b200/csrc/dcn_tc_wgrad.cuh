@@ -42,13 +42,20 @@ pack_dy(const Geom g, const float* __restrict__ dy, uint8_t* __restrict__ dpk, i
     if (ok0) g.d_ov.divmod((uint32_t)P0, n0, op0);
     if (ok1) g.d_ov.divmod((uint32_t)(P0 + 1), n1, op1);
     float mx = 0.f;
+    // both positions in one sample and 8-byte aligned (even ov, aligned dy): one 8-byte load per row
+    const bool pair = ok1 && n0 == n1 && (g.ov & 1) == 0 && (reinterpret_cast<uintptr_t>(dy) & 7) == 0;
     for (int row = wrp; row < 128; row += 8) {      // (forcing this loop to unroll 8-fold measured 20 % slower)
         const int ol = mt * 128 + row;
         float a = 0.f, b = 0.f;
         if (ol < g.Og) {
             const int o = j * g.Og + ol;
-            if (ok0) a = __ldg(dy + ((size_t)n0 * g.O + o) * g.ov + op0);
-            if (ok1) b = __ldg(dy + ((size_t)n1 * g.O + o) * g.ov + op1);
+            if (pair) {
+                const float2 t = __ldg(reinterpret_cast<const float2*>(dy + ((size_t)n0 * g.O + o) * g.ov + op0));
+                a = t.x; b = t.y;
+            } else {
+                if (ok0) a = __ldg(dy + ((size_t)n0 * g.O + o) * g.ov + op0);
+                if (ok1) b = __ldg(dy + ((size_t)n1 * g.O + o) * g.ov + op1);
+            }
         }
         mx = fmaxf(mx, fmaxf(fabsf(a), fabsf(b)));
         const uint32_t chunk = lane / 4;            // 8 positions per 16-byte chunk
