@@ -72,6 +72,25 @@ def test_shape_contract(L):
     assert L.dcn_workspace_bytes(ctypes.byref(ok), 0) == 0       # EXACT precision needs no scratch
 
 
+def test_sizes_beyond_the_32_bit_index_range_are_refused(L):
+    """The kernels index positions, input elements of a sample and offset channels with 32-bit integers (the reference
+    does too: `int` everywhere in deform3d/lib/deform_conv3d_cuda_kernel.cu:62-131); sizes past that are refused on
+    the host with DCN_ERR_LIMIT instead of overflowing on the device."""
+    big_batch = _p(N=70000, in_size=(256, 256), pad=(1, 1))                       # N * ov >= 2^31
+    assert L.dcn_validate(ctypes.byref(big_batch)) == -8
+    big_plane = _lib.make_problem(3, torch.float32, 1, 2048, 8, (64, 256, 256), (1, 1, 1), (1, 1, 1), (0, 0, 0),
+                                  (1, 1, 1), 1, 2048)                               # C * iv >= 2^31
+    assert L.dcn_validate(ctypes.byref(big_plane)) == -8
+    many_offsets = _lib.make_problem(3, torch.float32, 1, 64, 8, (32, 128, 128), (3, 3, 3), (1, 1, 1), (1, 1, 1),
+                                     (1, 1, 1), 1, 1)                               # dg * kv * 3 * ov >= 2^31
+    assert L.dcn_validate(ctypes.byref(many_offsets)) == -8
+    assert L.dcn_status_string(-8).decode().startswith("problem exceeds")
+    assert L.dcn_workspace_bytes(ctypes.byref(big_batch), 0) == 0 and L.dcn_launch_count(ctypes.byref(big_batch), 0) == 0
+    # the largest benchmark configuration is far inside the range
+    cfg3 = _lib.make_problem(3, torch.float32, 8, 64, 64, (16, 56, 56), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 64)
+    assert L.dcn_validate(ctypes.byref(cfg3)) == 0
+
+
 def test_null_pointers_are_refused_before_any_launch(L):
     ok = _p()
     assert L.dcn_forward(ctypes.byref(ok), None, None, None, None, None, None, 0, None) == -1
