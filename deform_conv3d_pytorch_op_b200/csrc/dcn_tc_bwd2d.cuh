@@ -246,7 +246,9 @@ struct B2Ctl {
 
 // ACC: dX accumulates into the caller's buffer (separate backward-data entry point); otherwise this kernel
 // zero-fills the part of dX it owns before it adds to it.
-template <bool ACC>
+// FULL: both gradients are wanted and the tap count is a whole number of tap groups per warp residue (the common
+// case: 3 x 3), so the per-tap tests of those conditions fold away at compile time.
+template <bool ACC, bool FULL>
 __global__ void __launch_bounds__(kB2Threads, 1)
 tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4* __restrict__ pts,
                 const uint8_t* __restrict__ dpk, const uint8_t* __restrict__ wpk,
@@ -361,8 +363,8 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
         const uint32_t plane_s = smem_u32(plane);
         const uint32_t xs_s = smem_u32(xs);
         const int W = g.in[2], Wp = d.Wp;
-        const bool want_dx = dx != nullptr;
-        const bool want_off = doff != nullptr;
+        const bool want_dx = FULL || dx != nullptr;
+        const bool want_off = FULL || doff != nullptr;
         const uint32_t lane_j = (uint32_t)lane & 7u, lane_g = (uint32_t)lane >> 3;
         uint32_t ck4[8];                                // byte offset of this lane's channel in step k
 #pragma unroll
@@ -412,7 +414,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
 #pragma unroll
                 for (int u = 0; u < TG; ++u) {
                     const int tap = tg + WQ * u;
-                    ent[u] = (in && tap < g.kv) ? __ldg(pts_n + (uint32_t)tap * (uint32_t)g.ov + (uint32_t)(P - pbeg))
+                    ent[u] = (in && (FULL || tap < g.kv)) ? __ldg(pts_n + (uint32_t)tap * (uint32_t)g.ov + (uint32_t)(P - pbeg))
                                                 : make_uint4(0u, 0u, 0u, 0u);
                 }
             };
@@ -483,7 +485,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
                     for (int u = 0; u < TG; ++u) {
                         uint32_t v[8];
                         const int tap = tg + WQ * u;
-                        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + b * 128 + (tap < g.kv ? tap : 0) * 8, v);
+                        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + b * 128 + ((FULL || tap < g.kv) ? tap : 0) * 8, v);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) f[u][i] = __uint_as_float(v[i]);
                     }
@@ -517,7 +519,7 @@ tc_bwd2d_kernel(const Geom g, const __nv_bfloat16* __restrict__ xcl, const uint4
 #pragma unroll
                     for (int u = 0; u < TG; ++u) {
                         const int tap = tg + WQ * u;
-                        if (tap >= g.kv) break;                 // warp-uniform
+                        if (!FULL && tap >= g.kv) break;        // warp-uniform
                         const bool sh = tp[u].sh, sw = tp[u].sw;
                         const float lw0 = tp[u].lw0, lw1 = tp[u].lw1, hw0 = 1.f - lw0, hw1 = 1.f - lw1;
                         if (want_off) {
@@ -647,14 +649,15 @@ int launch_tc_bwd2d(const Geom& g, const __nv_bfloat16* xcl, const uint4* pts, c
     d_iw.init((uint32_t)g.in[2]);
     d_w2.init((uint32_t)d.W2);
     const int grid = (int)(d.items < sm_count() ? d.items : sm_count());
-    if (accumulate) {
-        auto kern = tc_bwd2d_kernel<true>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bytes) != cudaSuccess) return -5;
+    const bool full = dx != nullptr && doff != nullptr && g.kv % (kB2WQ * 3) == 0;
+    auto go = [&](auto kern) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bytes) != cudaSuccess) return false;
         kern<<<grid, kB2Threads, d.smem_bytes, st>>>(g, xcl, pts, dpk, wpk, scale_bits, dx, doff, d, d_iw, d_w2);
-    } else {
-        auto kern = tc_bwd2d_kernel<false>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bytes) != cudaSuccess) return -5;
-        kern<<<grid, kB2Threads, d.smem_bytes, st>>>(g, xcl, pts, dpk, wpk, scale_bits, dx, doff, d, d_iw, d_w2);
-    }
+        return true;
+    };
+    bool launched;
+    if (accumulate) launched = full ? go(tc_bwd2d_kernel<true, true>) : go(tc_bwd2d_kernel<true, false>);
+    else launched = full ? go(tc_bwd2d_kernel<false, true>) : go(tc_bwd2d_kernel<false, false>);
+    if (!launched) return -5;
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
