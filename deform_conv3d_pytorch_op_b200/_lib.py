@@ -43,7 +43,7 @@ GENERIC_SYMBOLS = [
     "dcn_workspace_bytes", "dcn_launch_count", "dcn_forward", "dcn_backward_data", "dcn_backward_weight", "dcn_backward", "dcn_debug_points",
     "dcn_debug_tc_points", "dcn_debug_expire_wait",
     "dcn_check_status", "dcn_static_scratch_bytes", "dcn_forward_static_scratch",
-    "dcn_offset_conv_problem", "dcn_layer_workspace_bytes", "dcn_layer_forward", "dcn_layer_backward",
+    "dcn_offset_conv_problem", "dcn_layer_workspace_bytes", "dcn_layer_forward", "dcn_layer_backward", "dcn_layer_launch_count",
 ]
 LEGACY_SYMBOLS = [
     "dcn_deform3d_deform_conv_forward_cuda", "dcn_deform3d_deform_conv_backward_input_offset_cuda",
@@ -88,6 +88,7 @@ def lib() -> ctypes.CDLL:
         L.dcn_offset_conv_problem.argtypes = [pp, pp]
         L.dcn_layer_workspace_bytes.restype = ctypes.c_size_t
         L.dcn_layer_workspace_bytes.argtypes = [pp, ctypes.c_int]
+        L.dcn_layer_launch_count.argtypes = [pp, ctypes.c_int]
         L.dcn_layer_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         L.dcn_layer_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, ctypes.c_size_t, vp]
         _lib = L

@@ -354,6 +354,26 @@ size_t dcn_layer_workspace_bytes(const dcn_problem* p, int pass) {
     return dcn::tc_layer_workspace_bytes(g, gq, p->ndim, pass == DCN_PASS_FORWARD ? 0 : 3);
 }
 
+int dcn_layer_launch_count(const dcn_problem* p, int pass) {
+    dcn_problem q;
+    if (dcn_offset_conv_problem(p, &q) != DCN_OK) return 0;
+    Geom g, gq;
+    make_geom(p, g);
+    make_geom(&q, gq);
+    if (pass == DCN_PASS_FORWARD) {
+        if (p->precision == DCN_PREC_EXACT && dcn::simt_small_layer_supported(g, gq, p->dtype, p->ndim)) return 1;
+        // (bf16: the input copy is built once for both convolutions)
+        const int both = dcn_launch_count(&q, DCN_PASS_FORWARD) + dcn_launch_count(p, DCN_PASS_FORWARD);
+        return p->precision == DCN_PREC_BF16 && both > 0 ? both - 1 : both;
+    }
+    if (pass != DCN_PASS_BACKWARD) return 0;
+    const int main = dcn_launch_count(p, DCN_PASS_BACKWARD);
+    const int rest = dcn_launch_count(&q, DCN_PASS_BACKWARD_DATA) + dcn_launch_count(&q, DCN_PASS_BACKWARD_WEIGHT);
+    if (main == 0 || rest == 0) return 0;
+    // bf16: the plain convolution's two gradient kernels share the packed dOffset and take the input copy over
+    return p->precision == DCN_PREC_BF16 ? main + rest - 2 : main + rest;
+}
+
 int dcn_layer_forward(const dcn_problem* p, const void* x, const void* offset_weight, const void* offset_bias,
                       const void* weight, const void* bias, void* offset, void* y, void* ws, size_t ws_bytes,
                       void* stream) {
@@ -365,6 +385,12 @@ int dcn_layer_forward(const dcn_problem* p, const void* x, const void* offset_we
     const int a = check_ptrs(p, {x, offset_weight, offset_bias, weight, bias, offset, y});
     if (a != DCN_OK) return a;
     if (p->precision == DCN_PREC_EXACT) {
+        Geom g, gq;
+        make_geom(p, g);
+        make_geom(&q, gq);
+        if (dcn::simt_small_layer_supported(g, gq, p->dtype, p->ndim))      // one kernel, offsets formed on the SM
+            return dcn::simt_small_layer_forward(g, gq, p->ndim, x, offset_weight, offset_bias, weight, bias, offset, y,
+                                                 static_cast<cudaStream_t>(stream));
         const int r = dcn_forward(&q, x, nullptr, offset_weight, offset_bias, offset, nullptr, 0, stream);
         if (r != DCN_OK) return r;
         return dcn_forward(p, x, offset, weight, bias, y, nullptr, 0, stream);

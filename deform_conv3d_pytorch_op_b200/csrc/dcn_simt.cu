@@ -617,6 +617,16 @@ int simt_small_forward(const Geom& g, int ndim, const void* x, const void* off, 
     return launch_small_forward<3>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)bias, (float*)y, st);
 }
 
+bool simt_small_layer_supported(const Geom& g, const Geom& gq, int dtype, int ndim) {
+    return small_layer_supported(g, gq, dtype, ndim);
+}
+
+int simt_small_layer_forward(const Geom& g, const Geom& gq, int ndim, const void* x, const void* w_off, const void* b_off,
+                             const void* w, const void* bias, void* offsets, void* y, cudaStream_t st) {
+    if (ndim == 2) return launch_small_layer_forward<2>(g, gq, (const float*)x, (const float*)w_off, (const float*)b_off, (const float*)w, (const float*)bias, (float*)offsets, (float*)y, st);
+    return launch_small_layer_forward<3>(g, gq, (const float*)x, (const float*)w_off, (const float*)b_off, (const float*)w, (const float*)bias, (float*)offsets, (float*)y, st);
+}
+
 int simt_small_backward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* dy,
                         void* dx, void* doff, void* dw, cudaStream_t st) {
     if (ndim == 2) return launch_small_backward<2>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)dy, (float*)dx, (float*)doff, (float*)dw, st);

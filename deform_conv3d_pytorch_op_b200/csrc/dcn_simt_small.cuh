@@ -148,6 +148,177 @@ small_forward_kernel(const Geom g, const float* __restrict__ x, const float* __r
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Fused layer forward for small problems: the offsets are computed INSIDE the kernel, from the plain (integer-tap,
+// dilation 1) patch of the CTA's positions and the offset-producing convolution's weights, and stay in shared
+// memory for the sampling that follows; they are also written out once, because the backward pass reads them.
+// gq: geometry of the offset-producing convolution (one group, dg*kv*D output channels, dilation 1).
+// Extra shared memory behind the forward kernel's: plain patch [TP][C*kv], offsets [ndg][kv][D][TP], the rows of the
+// offset weights of this CTA's deformable groups.
+// ---------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(kSmallThreads)
+small_layer_forward_kernel(const Geom g, const Geom gq, const float* __restrict__ x, const float* __restrict__ w_off,
+                           const float* __restrict__ b_off, const float* __restrict__ w,
+                           const float* __restrict__ bias, float* __restrict__ offsets, float* __restrict__ y,
+                           const int TP, const int ndg) {
+    extern __shared__ float sm_small[];
+    float* Ws = sm_small;                                 // [Og][Kg]
+    float* smp = Ws + g.Og * g.Kg;                        // [TP][Kg + 1]
+    float* pts = smp + TP * (g.Kg + 1);                   // [ndg][kv][TP][D + 1]
+    float* pp = pts + TP * g.kv * ndg * (D + 1);          // [TP][Kq + 1] plain patch of all C channels
+    float* offs = pp + TP * (gq.Kg + 1);                  // [ndg][kv][D][TP]
+    float* Wq = offs + ndg * g.kv * D * TP;               // [ndg * kv * D][Kq] rows of the offset weights this CTA needs
+    const int j = blockIdx.y;
+    const long long P0 = (long long)blockIdx.x * TP;
+    const int Kq = gq.Kg;                                 // C * kv
+    int grp0, n_;
+    small_dg_range(g, j, grp0, n_);
+    for (int i = threadIdx.x; i < g.Og * g.Kg; i += kSmallThreads) Ws[i] = __ldg(w + (size_t)j * g.Og * g.Kg + i);
+    // the offset channels of this CTA's deformable groups are consecutive rows of the offset weights
+    for (int i = threadIdx.x; i < n_ * g.kv * D * Kq; i += kSmallThreads)
+        Wq[i] = __ldg(w_off + (size_t)grp0 * g.kv * D * Kq + i);
+    // plain patch: x at the integer taps of the offset-producing convolution
+    for (int it = threadIdx.x; it < TP * Kq; it += kSmallThreads) {
+        const int pl = it % TP, k = it / TP;
+        const long long P = P0 + pl;
+        float v = 0.f;
+        if (P < g.P) {
+            uint32_t c, tap;
+            g.d_kv.divmod((uint32_t)k, c, tap);
+            const OutPos op = decompose_pos(gq, P);
+            int idx;
+            if (locate_plain<D>(gq, (int)tap, op, idx)) v = __ldg(x + ((size_t)op.n * g.C + c) * g.iv + idx);
+        }
+        pp[pl * (Kq + 1) + k] = v;
+    }
+    __syncthreads();
+    // offsets of the deformable groups this convolution group touches: one warp per (offset channel, position) pair,
+    // lanes over the contraction index
+    {
+        const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+        const int per_grp = g.kv * D;
+        for (int item = warp; item < n_ * per_grp * TP; item += kSmallThreads / 32) {
+            const int pl = item % TP, r = item / TP;            // r = gl * kv * D + tap * D + a
+            const int oc = grp0 * per_grp + r;                  // offset channel ((grp * kv + tap) * D + a)
+            const float* wr = Wq + (size_t)r * Kq;
+            const float* pr = pp + pl * (Kq + 1);
+            float acc = 0.f;
+            for (int k = lane; k < Kq; k += 32) acc = fmaf(wr[k], pr[k], acc);
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+            if (lane == 0) {
+                const float v = acc + (b_off != nullptr ? __ldg(b_off + oc) : 0.f);
+                offs[r * TP + pl] = v;
+                const long long P = P0 + pl;
+                if (P < g.P && offsets != nullptr) {
+                    uint32_t n, opos;
+                    g.d_ov.divmod((uint32_t)P, n, opos);
+                    offsets[((size_t)n * gq.O + oc) * g.ov + opos] = v;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // sampling points from the offsets in shared memory (same rule: locate_with)
+    for (int e = threadIdx.x; e < TP * g.kv * ndg; e += kSmallThreads) {
+        const int pl = e % TP, r = e / TP, tap = r % g.kv, gl = r / g.kv;
+        float* dst = pts + (size_t)e * (D + 1);
+        const long long P = P0 + pl;
+        bool ok = false;
+        if (P < g.P && gl < n_) {
+            const OutPos op = decompose_pos(g, P);
+            float offv[D];
+#pragma unroll
+            for (int a = 0; a < D; ++a) offv[a] = offs[((gl * g.kv + tap) * D + a) * TP + pl];
+            Pt<float, D> s;
+            locate_with<float, D>(g, offv, tap, op, s);
+#pragma unroll
+            for (int a = 0; a < D; ++a) dst[a] = s.p[a];
+            ok = true;
+        }
+        dst[D] = ok ? 1.f : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int it = threadIdx.x; it < TP * g.Kg; it += kSmallThreads) {
+        const int pl = it % TP, k = it / TP;
+        uint32_t cl, tap;
+        g.d_kv.divmod((uint32_t)k, cl, tap);
+        const int c = j * g.Cg + (int)cl;
+        const int gl = (int)g.d_cpg.div((uint32_t)c) - grp0;
+        Pt<float, D> s;
+        float val = 0.f;
+        if (small_load_point<D>(g, pts, (gl * g.kv + (int)tap) * TP + pl, s) && s.valid) {
+            uint32_t n = g.d_ov.div((uint32_t)(P0 + pl));
+            const float* plane = x + ((size_t)n * g.C + c) * g.iv;
+            int idx[1 << D];
+            corner_indices<float, D>(g, s, idx);
+            float cv[1 << D];
+#pragma unroll
+            for (int i = 0; i < (1 << D); ++i) cv[i] = __ldg(plane + idx[i]);
+            val = interp<float, D>(s, cv);
+        }
+        smp[pl * (g.Kg + 1) + k] = val;
+    }
+    __syncthreads();
+    const int outs = TP * g.Og;
+    int S = 1;
+    while (S < 8 && outs * (S * 2) <= kSmallThreads) S *= 2;
+    for (int base = 0; base < outs * S; base += kSmallThreads) {
+        const int t = base + (int)threadIdx.x;
+        const int it = t / S, sub = t % S;
+        const bool live = it < outs;
+        const int pl = live ? it % TP : 0, ol = live ? it / TP : 0;
+        const float* wr = Ws + ol * g.Kg;
+        const float* sr = smp + pl * (g.Kg + 1);
+        float a2[2] = {0.f, 0.f};
+        int k = sub;
+        for (; k + S < g.Kg; k += 2 * S) {
+            a2[0] = fmaf(wr[k], sr[k], a2[0]);
+            a2[1] = fmaf(wr[k + S], sr[k + S], a2[1]);
+        }
+        if (k < g.Kg) a2[0] = fmaf(wr[k], sr[k], a2[0]);
+        float acc = a2[0] + a2[1];
+        for (int m = S / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        const long long P = P0 + pl;
+        if (!live || sub != 0 || P >= g.P) continue;
+        uint32_t n, opos;
+        g.d_ov.divmod((uint32_t)P, n, opos);
+        const int o = j * g.Og + ol;
+        y[((size_t)n * g.O + o) * g.ov + opos] = acc + (bias != nullptr ? __ldg(bias + o) : 0.f);
+    }
+}
+
+inline bool small_supported(const Geom& g, int dtype, int ndim, int deform);
+
+inline size_t small_layer_smem(const Geom& g, const Geom& gq, int D) {
+    const SmallDims d = small_dims(g, D);
+    return (size_t)d.smem_fwd + 4 * ((size_t)d.TP * (gq.Kg + 1) + (size_t)d.ndg * g.kv * D * d.TP +
+                                     (size_t)d.ndg * g.kv * D * gq.Kg);
+}
+
+// the fused layer forward: a small problem whose plain patch also fits, with the same output positions for both
+// convolutions (which dcn_offset_conv_problem guarantees)
+inline bool small_layer_supported(const Geom& g, const Geom& gq, int dtype, int ndim) {
+    if (!small_supported(g, dtype, ndim, 1)) return false;
+    if ((double)g.P * gq.Kg * gq.O > 16777216.0) return false;
+    return small_layer_smem(g, gq, ndim) <= 96 * 1024 && gq.ov == g.ov && gq.P == g.P;
+}
+
+template <int D>
+int launch_small_layer_forward(const Geom& g, const Geom& gq, const float* x, const float* w_off, const float* b_off,
+                               const float* w, const float* bias, float* offsets, float* y, cudaStream_t st) {
+    const SmallDims d = small_dims(g, D);
+    const int smem = (int)small_layer_smem(g, gq, D);
+    auto kern = small_layer_forward_kernel<D>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -5;
+    dim3 grid((unsigned)((g.P + d.TP - 1) / d.TP), (unsigned)g.G);
+    kern<<<grid, kSmallThreads, smem, st>>>(g, gq, x, w_off, b_off, w, bias, offsets, y, d.TP, d.ndg);
+    return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 // dx and dw must be zero-filled by the launch before this one (see launch_small_backward); doff is written with
 // plain stores when DOFF_PLAIN (one conv group: a CTA then holds every channel of the deformable groups it touches),
 // else added to a zero-filled doff.

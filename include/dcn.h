@@ -175,6 +175,12 @@ int dcn_offset_conv_problem(const dcn_problem* p, dcn_problem* q);
 /* Scratch bytes of dcn_layer_forward (pass = DCN_PASS_FORWARD) / dcn_layer_backward (DCN_PASS_BACKWARD). */
 size_t dcn_layer_workspace_bytes(const dcn_problem* p, int pass);
 
+/* Kernel launches of dcn_layer_forward / dcn_layer_backward when every gradient is wanted (memsets not counted).
+ * A small fp32 problem under precision EXACT takes ONE forward launch: the offsets are formed inside the kernel,
+ * from the plain patch of the CTA's positions, and stay in shared memory for the sampling that follows (they are
+ * written out once, for the backward pass). */
+int dcn_layer_launch_count(const dcn_problem* p, int pass);
+
 /* offset = conv(x, offset_weight) + offset_bias;  y = deform_conv(x, offset, weight) + bias.
  * `offset` (written) and `y` (written) are caller buffers; keep `offset` for the backward pass.
  * BF16: the channels-last bf16 copy of x is left at the START of the workspace, as dcn_forward does. */

@@ -84,3 +84,25 @@ def test_bf16_path_on_random_geometries(case):
         if k == "doff":
             a, r = np.where(mask, 0, a), np.where(mask, 0, r)
         assert cases.rel_err(a, r) <= 2e-2, (k, cases.rel_err(a, r), case)
+
+
+@pytest.mark.parametrize("case", _cases(4242, 16, False), ids=lambda c: c.name)
+def test_layer_forward_on_random_geometries(case):
+    """The single-kernel layer forward (offsets formed in the kernel) against torch's fp32 convolution for the
+    offsets and the library's own deformable Function, itself oracle-checked above, for y (fp32 gate 1e-4)."""
+    import torch
+    import deform_conv3d_pytorch_op_b200 as dcn
+    x, w, off, dy, b = [None if t is None else t.cuda() for t in cases.make_inputs(case)]
+    op = dcn.Op(x, w, case.stride, case.pad, case.dil, case.cpg, case.G)
+    g = torch.Generator().manual_seed(3)
+    w_off = (torch.randn(op.offset_weight_shape(), generator=g) * 0.2).cuda()
+    b_off = (torch.randn(op.offset_channels, generator=g) * 0.5).cuda()
+    y, offsets = op.layer_forward(x, w_off, b_off, w, b)
+    conv = torch.nn.functional.conv3d if case.ndim == 3 else torch.nn.functional.conv2d
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        off_ref = conv(x, w_off, b_off, stride=case.stride, padding=case.pad)
+    assert offsets.shape == off_ref.shape
+    assert cases.rel_err(offsets.cpu().numpy(), off_ref.cpu().numpy()) <= 1e-5
+    fn = dcn.ConvOffset3dFunction if case.ndim == 3 else dcn.ConvOffset2dFunction
+    y_ref = fn.apply(x, offsets, w, b, case.stride, case.pad, case.dil, case.cpg, case.G)
+    assert cases.rel_err(y.cpu().numpy(), y_ref.cpu().numpy()) <= 1e-4
