@@ -367,6 +367,7 @@ int dcn_layer_launch_count(const dcn_problem* p, int pass) {
         return p->precision == DCN_PREC_BF16 && both > 0 ? both - 1 : both;
     }
     if (pass != DCN_PASS_BACKWARD) return 0;
+    if (p->precision == DCN_PREC_EXACT && dcn::simt_small_layer_supported(g, gq, p->dtype, p->ndim)) return 2;
     const int main = dcn_launch_count(p, DCN_PASS_BACKWARD);
     const int rest = dcn_launch_count(&q, DCN_PASS_BACKWARD_DATA) + dcn_launch_count(&q, DCN_PASS_BACKWARD_WEIGHT);
     if (main == 0 || rest == 0) return 0;
@@ -422,6 +423,16 @@ int dcn_layer_backward(const dcn_problem* p, const void* x, const void* offset, 
     make_geom(&q, gq);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool chain = dx != nullptr || doffset_weight != nullptr || doffset_bias != nullptr;
+    if (p->precision == DCN_PREC_EXACT && dcn::simt_small_layer_supported(g, gq, p->dtype, p->ndim)) {
+        // one zero fill + one kernel: the offset gradient stays in shared memory and is pushed through the
+        // offset-producing convolution there
+        int r = DCN_OK;
+        if (dx != nullptr || doffset_weight != nullptr || doffset_bias != nullptr || dweight != nullptr)
+            r = dcn::simt_small_layer_backward(g, gq, p->ndim, x, offset, offset_weight, weight, dy, dx, doffset_weight,
+                                               doffset_bias, dweight, st);
+        if (r == DCN_OK && dbias != nullptr) r = dcn::bias_grad(g, p->dtype, dy, dbias, st);
+        return r;
+    }
     if (p->precision == DCN_PREC_EXACT) {
         if (chain && !workspace_ok(ws, ws_bytes, layer_doff_bytes(p, g))) return DCN_ERR_WORKSPACE;
         void* doff = chain ? ws : nullptr;

@@ -26,6 +26,9 @@ int simt_small_backward(const Geom& g, int ndim, const void* x, const void* off,
 bool simt_small_layer_supported(const Geom& g, const Geom& gq, int dtype, int ndim);
 int simt_small_layer_forward(const Geom& g, const Geom& gq, int ndim, const void* x, const void* w_off, const void* b_off,
                              const void* w, const void* bias, void* offsets, void* y, cudaStream_t st);
+int simt_small_layer_backward(const Geom& g, const Geom& gq, int ndim, const void* x, const void* offsets,
+                              const void* w_off, const void* w, const void* dy, void* dx, void* dw_off, void* db_off,
+                              void* dw, cudaStream_t st);
 bool simt_backward_both_supported(const Geom& g, int dtype);
 int simt_backward_both(const Geom& g, int ndim, int deform, const void* x, const void* off, const void* w,
                        const void* dy, void* dx, void* doff, void* dw, cudaStream_t st);

@@ -627,6 +627,14 @@ int simt_small_layer_forward(const Geom& g, const Geom& gq, int ndim, const void
     return launch_small_layer_forward<3>(g, gq, (const float*)x, (const float*)w_off, (const float*)b_off, (const float*)w, (const float*)bias, (float*)offsets, (float*)y, st);
 }
 
+int simt_small_layer_backward(const Geom& g, const Geom& gq, int ndim, const void* x, const void* offsets,
+                              const void* w_off, const void* w, const void* dy, void* dx, void* dw_off, void* db_off,
+                              void* dw, cudaStream_t st) {
+    const SmallLayer lay{(const float*)w_off, (float*)dw_off, (float*)db_off};
+    if (ndim == 2) return launch_small_backward<2>(g, (const float*)x, (const float*)offsets, (const float*)w, (const float*)dy, (float*)dx, nullptr, (float*)dw, st, &gq, &lay);
+    return launch_small_backward<3>(g, (const float*)x, (const float*)offsets, (const float*)w, (const float*)dy, (float*)dx, nullptr, (float*)dw, st, &gq, &lay);
+}
+
 int simt_small_backward(const Geom& g, int ndim, const void* x, const void* off, const void* w, const void* dy,
                         void* dx, void* doff, void* dw, cudaStream_t st) {
     if (ndim == 2) return launch_small_backward<2>(g, (const float*)x, (const float*)off, (const float*)w, (const float*)dy, (float*)dx, (float*)doff, (float*)dw, st);

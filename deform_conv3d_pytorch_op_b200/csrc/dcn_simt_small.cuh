@@ -303,7 +303,9 @@ inline size_t small_layer_smem(const Geom& g, const Geom& gq, int D) {
 inline bool small_layer_supported(const Geom& g, const Geom& gq, int dtype, int ndim) {
     if (!small_supported(g, dtype, ndim, 1)) return false;
     if ((double)g.P * gq.Kg * gq.O > 16777216.0) return false;
-    return small_layer_smem(g, gq, ndim) <= 96 * 1024 && gq.ov == g.ov && gq.P == g.P;
+    const SmallDims d = small_dims(g, ndim);
+    const size_t bwd = (size_t)d.smem_bwd + 4 * ((size_t)d.TP * (gq.Kg + 1) + (size_t)d.ndg * g.kv * ndim * gq.Kg);
+    return small_layer_smem(g, gq, ndim) <= 96 * 1024 && bwd <= 96 * 1024 && gq.ov == g.ov && gq.P == g.P;
 }
 
 template <int D>
@@ -322,17 +324,31 @@ int launch_small_layer_forward(const Geom& g, const Geom& gq, const float* x, co
 // dx and dw must be zero-filled by the launch before this one (see launch_small_backward); doff is written with
 // plain stores when DOFF_PLAIN (one conv group: a CTA then holds every channel of the deformable groups it touches),
 // else added to a zero-filled doff.
-template <int D, bool DOFF_PLAIN>
+// LAYER: the backward pass of the whole layer (offset-producing convolution + deformable convolution) in this one
+// launch.  The offset gradient then is no output: it stays in the shared-memory accumulators and is pushed through
+// the offset-producing convolution here -- its bias and weight gradients from the plain patch of the CTA's positions,
+// its input gradient added to dx at the integer taps.  `lay` carries that convolution (gq: its geometry).
+struct SmallLayer {
+    const float* w_off;      // [dg*kv*D][C*kv]
+    float* dw_off;           // zero-filled before this launch; may be null
+    float* db_off;           // zero-filled before this launch; may be null
+};
+
+template <int D, bool DOFF_PLAIN, bool LAYER>
 __global__ void __launch_bounds__(kSmallThreads)
 small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __restrict__ off,
                       const float* __restrict__ w, const float* __restrict__ dy, float* __restrict__ dx,
-                      float* __restrict__ doff, float* __restrict__ dw, const int TP, const int ndg) {
+                      float* __restrict__ doff, float* __restrict__ dw, const int TP, const int ndg,
+                      const Geom gq, const SmallLayer lay) {
     extern __shared__ float sm_small[];
     float* Ws = sm_small;                                 // [Og][Kg]
     float* dys = Ws + g.Og * g.Kg;                        // [Og][TP]
     float* smp = dys + g.Og * TP;                         // [TP][Kg + 1]
     float* pts = smp + TP * (g.Kg + 1);                   // [ndg][kv][TP][D + 1]
     float* dacc = pts + TP * g.kv * ndg * (D + 1);        // [ndg][kv][TP][D]
+    float* pp = dacc + TP * g.kv * ndg * D;               // LAYER: [TP][Kq + 1] plain patch, all C channels
+    float* Wq = pp + (LAYER ? TP * (gq.Kg + 1) : 0);      // LAYER: [ndg * kv * D][Kq] offset-weight rows of this CTA
+    const bool want_doff = LAYER || doff != nullptr;
     const int j = blockIdx.y;
     const long long P0 = (long long)blockIdx.x * TP;
     int grp0, n_;
@@ -350,6 +366,24 @@ small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __
         dys[ol * TP + pl] = v;
     }
     for (int i = threadIdx.x; i < TP * g.kv * ndg * D; i += kSmallThreads) dacc[i] = 0.f;
+    if (LAYER) {
+        const int Kq = gq.Kg;
+        for (int i = threadIdx.x; i < n_ * g.kv * D * Kq; i += kSmallThreads)
+            Wq[i] = __ldg(lay.w_off + (size_t)grp0 * g.kv * D * Kq + i);
+        for (int it = threadIdx.x; it < TP * Kq; it += kSmallThreads) {
+            const int pl = it % TP, k = it / TP;
+            const long long P = P0 + pl;
+            float v = 0.f;
+            if (P < g.P) {
+                uint32_t c, tap;
+                g.d_kv.divmod((uint32_t)k, c, tap);
+                const OutPos op = decompose_pos(gq, P);
+                int idx;
+                if (locate_plain<D>(gq, (int)tap, op, idx)) v = __ldg(x + ((size_t)op.n * g.C + c) * g.iv + idx);
+            }
+            pp[pl * (Kq + 1) + k] = v;
+        }
+    }
     small_points<D>(g, off, j, TP, ndg, P0, pts);
     __syncthreads();
     // Everything above only reads inputs.  The outputs are zero-filled by the launch before this one, which this
@@ -389,13 +423,13 @@ small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __
 #pragma unroll
                     for (int i = 0; i < (1 << D); ++i) atomicAdd(dx + pbase + idx[i], cw[i] * col);
                 }
-                if (doff != nullptr) {
+                if (want_doff) {
                     float gr[D];
                     interp_grad<float, D>(s, cv, gr);
 #pragma unroll
                     for (int a = 0; a < D; ++a) atomicAdd(dacc + (size_t)e * D + a, col * gr[a]);
                 }
-            } else if (D == 3 && g.oob && doff != nullptr) {
+            } else if (D == 3 && g.oob && want_doff) {
 #pragma unroll
                 for (int a = 0; a < D; ++a) {
                     const float t = oob_term<float>(g, s.p[a], col);
@@ -418,7 +452,42 @@ small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __
             if (acc != 0.f) atomicAdd(dw + ((size_t)j * g.Og + ol) * g.Kg + k, acc);
         }
     }
-    if (doff != nullptr) {
+    if (LAYER) {
+        // dacc row r = (gl * kv + tap) * D + a at position pl: dacc[((gl * kv + tap) * TP + pl) * D + a]
+        const int Kq = gq.Kg, rows = n_ * g.kv * D;
+        auto dval = [&](int r, int pl) { return dacc[((r / D) * TP + pl) * D + (r % D)]; };
+        if (lay.db_off != nullptr) {
+            for (int r = threadIdx.x; r < rows; r += kSmallThreads) {
+                float sum = 0.f;
+                for (int pl = 0; pl < TP; ++pl) sum += dval(r, pl);
+                if (sum != 0.f) atomicAdd(lay.db_off + grp0 * g.kv * D + r, sum);
+            }
+        }
+        if (lay.dw_off != nullptr) {
+            for (int it = threadIdx.x; it < rows * Kq; it += kSmallThreads) {
+                const int k = it % Kq, r = it / Kq;
+                float sum = 0.f;
+                for (int pl = 0; pl < TP; ++pl) sum = fmaf(dval(r, pl), pp[pl * (Kq + 1) + k], sum);
+                if (sum != 0.f) atomicAdd(lay.dw_off + (size_t)(grp0 * g.kv * D + r) * Kq + k, sum);
+            }
+        }
+        if (dx != nullptr) {
+            for (int it = threadIdx.x; it < TP * Kq; it += kSmallThreads) {
+                const int pl = it % TP, k = it / TP;
+                const long long P = P0 + pl;
+                if (P >= g.P) continue;
+                uint32_t c, tap;
+                g.d_kv.divmod((uint32_t)k, c, tap);
+                const OutPos op = decompose_pos(gq, P);
+                int idx;
+                if (!locate_plain<D>(gq, (int)tap, op, idx)) continue;
+                float sum = 0.f;
+                for (int r = 0; r < rows; ++r) sum = fmaf(Wq[(size_t)r * Kq + k], dval(r, pl), sum);
+                if (sum != 0.f) atomicAdd(dx + ((size_t)op.n * g.C + c) * g.iv + idx, sum);
+            }
+        }
+    }
+    if (!LAYER && doff != nullptr) {
         for (int i = threadIdx.x; i < TP * g.kv * ndg * D; i += kSmallThreads) {
             const int a = i % D, e = i / D;
             const int pl = e % TP, r = e / TP, tap = r % g.kv, gl = r / g.kv;
@@ -453,15 +522,19 @@ int launch_small_forward(const Geom& g, const float* x, const float* off, const 
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-// Zero fill of up to three output buffers in one launch; lets the dependent launch start at once.
+// Zero fill of up to five output buffers in one launch; lets the dependent launch start at once.
+struct ZeroList {
+    float4* p[5];
+    size_t n4[5];
+};
 __global__ void __launch_bounds__(256)
-small_zero_kernel(float4* __restrict__ a, size_t na4, float4* __restrict__ b, size_t nb4, float4* __restrict__ c, size_t nc4) {
+small_zero_kernel(const ZeroList z) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < na4; i += stride) a[i] = z;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nb4; i += stride) b[i] = z;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nc4; i += stride) c[i] = z;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int b = 0; b < 5; ++b)
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < z.n4[b]; i += stride) z.p[b][i] = zero;
 }
 
 inline bool small_pdl_enabled() {
@@ -469,51 +542,65 @@ inline bool small_pdl_enabled() {
     return !off;
 }
 
-// dX, dW (and dOffset with several convolution groups) are zero-filled here: by one kernel when the buffers allow
-// 16-byte stores, and then the main kernel is launched as its programmatic dependent, so that its input-only
-// prologue (weights, dy tile, sampling points) runs while the zero fill is still in flight.
+// dX, dW (dOffset with several convolution groups; the offset-producing convolution's gradients in layer mode) are
+// zero-filled here: by one kernel when the buffers allow 16-byte stores, and then the main kernel is launched as its
+// programmatic dependent, so that its input-only prologue (weights, dy tile, sampling points) runs while the zero
+// fill is still in flight.
+// lay / gq: null for the operator alone; else the layer's backward pass (doff is then not an output).
 template <int D>
 int launch_small_backward(const Geom& g, const float* x, const float* off, const float* w, const float* dy, float* dx,
-                          float* doff, float* dw, cudaStream_t st) {
+                          float* doff, float* dw, cudaStream_t st, const Geom* gq = nullptr,
+                          const SmallLayer* lay = nullptr) {
     const SmallDims d = small_dims(g, D);
+    const bool layer = lay != nullptr;
     dim3 grid((unsigned)((g.P + d.TP - 1) / d.TP), (unsigned)g.G);
-    const size_t ndx = dx != nullptr ? (size_t)g.N * g.C * g.iv : 0;
-    const size_t ndw = dw != nullptr ? (size_t)g.O * g.Cg * g.kv : 0;
-    const size_t ndo = (g.G > 1 && doff != nullptr) ? (size_t)g.N * g.dg * g.kv * D * g.ov : 0;
-    auto vec_ok = [](const void* p, size_t n) { return n % 4 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    bool pdl = small_pdl_enabled() && vec_ok(dx, ndx) && vec_ok(dw, ndw) && vec_ok(doff, ndo);
+    float* bufs[5] = {dx, dw, (!layer && g.G > 1) ? doff : nullptr, layer ? lay->dw_off : nullptr,
+                      layer ? lay->db_off : nullptr};
+    const size_t lens[5] = {(size_t)g.N * g.C * g.iv, (size_t)g.O * g.Cg * g.kv, (size_t)g.N * g.dg * g.kv * D * g.ov,
+                            layer ? (size_t)gq->O * gq->Kg : 0, layer ? (size_t)gq->O : 0};
+    bool pdl = small_pdl_enabled();
+    ZeroList z;
+    size_t most = 0;
+    for (int b = 0; b < 5; ++b) {
+        const size_t n = bufs[b] != nullptr ? lens[b] : 0;
+        if (n % 4 != 0 || (reinterpret_cast<uintptr_t>(bufs[b]) & 15) != 0) pdl = false;
+        z.p[b] = reinterpret_cast<float4*>(bufs[b]);
+        z.n4[b] = n / 4;
+        if (n / 4 > most) most = n / 4;
+    }
     if (pdl) {
-        const size_t most = (ndx > ndw ? ndx : ndw) / 4;
-        const int blocks = (int)((most + 255) / 256 < 296 ? ((most + 255) / 256 > 0 ? (most + 255) / 256 : 1) : 296);
-        small_zero_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<float4*>(dx), ndx / 4, reinterpret_cast<float4*>(dw),
-                                                  ndw / 4, reinterpret_cast<float4*>(doff), ndo / 4);
+        size_t blocks = (most + 255) / 256;
+        if (blocks < 1) blocks = 1;
+        if (blocks > 296) blocks = 296;
+        small_zero_kernel<<<(unsigned)blocks, 256, 0, st>>>(z);
         if (cudaGetLastError() != cudaSuccess) return -5;
     } else {
-        if (ndx != 0 && cudaMemsetAsync(dx, 0, ndx * sizeof(float), st) != cudaSuccess) return -5;
-        if (ndw != 0 && cudaMemsetAsync(dw, 0, ndw * sizeof(float), st) != cudaSuccess) return -5;
-        if (ndo != 0 && cudaMemsetAsync(doff, 0, ndo * sizeof(float), st) != cudaSuccess) return -5;
+        for (int b = 0; b < 5; ++b)
+            if (bufs[b] != nullptr && cudaMemsetAsync(bufs[b], 0, lens[b] * sizeof(float), st) != cudaSuccess) return -5;
     }
+    size_t smem = (size_t)d.smem_bwd;
+    if (layer) smem += 4 * ((size_t)d.TP * (gq->Kg + 1) + (size_t)d.ndg * g.kv * D * gq->Kg);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kSmallThreads);
-    cfg.dynamicSmemBytes = (size_t)d.smem_bwd;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    const Geom gq_v = layer ? *gq : g;
+    const SmallLayer lay_v = layer ? *lay : SmallLayer{nullptr, nullptr, nullptr};
+    auto go = [&](auto kern) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return cudaErrorInvalidValue;
+        return cudaLaunchKernelEx(&cfg, kern, g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg, gq_v, lay_v);
+    };
     cudaError_t e;
-    if (g.G == 1) {
-        auto kern = small_backward_kernel<D, true>;
-        if (d.smem_bwd > 48 * 1024 &&
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
-        e = cudaLaunchKernelEx(&cfg, kern, g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
-    } else {
-        auto kern = small_backward_kernel<D, false>;
-        if (d.smem_bwd > 48 * 1024 &&
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, d.smem_bwd) != cudaSuccess) return -5;
-        e = cudaLaunchKernelEx(&cfg, kern, g, x, off, w, dy, dx, doff, dw, d.TP, d.ndg);
-    }
+    if (layer) e = go(small_backward_kernel<D, true, true>);
+    else if (g.G == 1) e = go(small_backward_kernel<D, true, false>);
+    else e = go(small_backward_kernel<D, false, false>);
     return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -5;
 }

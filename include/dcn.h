@@ -178,7 +178,8 @@ size_t dcn_layer_workspace_bytes(const dcn_problem* p, int pass);
 /* Kernel launches of dcn_layer_forward / dcn_layer_backward when every gradient is wanted (memsets not counted).
  * A small fp32 problem under precision EXACT takes ONE forward launch: the offsets are formed inside the kernel,
  * from the plain patch of the CTA's positions, and stay in shared memory for the sampling that follows (they are
- * written out once, for the backward pass). */
+ * written out once, for the backward pass), and a zero-fill launch plus ONE backward launch in which the offset
+ * gradient stays in shared memory and is pushed through the offset-producing convolution in place. */
 int dcn_layer_launch_count(const dcn_problem* p, int pass);
 
 /* offset = conv(x, offset_weight) + offset_bias;  y = deform_conv(x, offset, weight) + bias.

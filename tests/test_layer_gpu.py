@@ -66,6 +66,7 @@ def test_layer_equals_its_two_halves_fp32(ndim, N, C, O, size, k, stride, pad, d
     from deform_conv3d_pytorch_op_b200 import _lib
     op = dcn.Op(x, c.weight, c.stride, c.padding, c.dilation, c.channel_per_group, c.group)
     assert _lib.lib().dcn_layer_launch_count(ctypes.byref(op.p), _lib.PASS_FORWARD) == 1
+    assert _lib.lib().dcn_layer_launch_count(ctypes.byref(op.p), _lib.PASS_BACKWARD) == 2     # zero fill + one kernel
     y2, off2 = op.layer_forward(x.detach(), m.conv_offset.weight, m.conv_offset.bias, c.weight, c.bias)
     assert _rel(off2, off) <= 1e-5 and _rel(y2, ref) <= TOL_FP32
 
