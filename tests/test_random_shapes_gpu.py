@@ -106,3 +106,32 @@ def test_layer_forward_on_random_geometries(case):
     fn = dcn.ConvOffset3dFunction if case.ndim == 3 else dcn.ConvOffset2dFunction
     y_ref = fn.apply(x, offsets, w, b, case.stride, case.pad, case.dil, case.cpg, case.G)
     assert cases.rel_err(y.cpu().numpy(), y_ref.cpu().numpy()) <= 1e-4
+
+
+@pytest.mark.parametrize("case", _cases(5150, 12, False), ids=lambda c: c.name)
+def test_layer_backward_on_random_geometries(case):
+    """All five gradients of the single-kernel layer backward (offset gradient kept in shared memory) against
+    autograd through torch's fp32 convolution followed by the library's deformable Function."""
+    import torch
+    import deform_conv3d_pytorch_op_b200 as dcn
+    x, w, off, dy, b = [None if t is None else t.cuda() for t in cases.make_inputs(case)]
+    op = dcn.Op(x, w, case.stride, case.pad, case.dil, case.cpg, case.G)
+    g = torch.Generator().manual_seed(4)
+    w_off = (torch.randn(op.offset_weight_shape(), generator=g) * 0.2).cuda()
+    b_off = (torch.randn(op.offset_channels, generator=g) * 0.5).cuda()
+    if b is None:
+        b = torch.zeros(case.O, device="cuda")
+    params = [t.clone().requires_grad_(True) for t in (x, w_off, b_off, w, b)]
+    y = dcn.DeformLayerFunction.apply(params[0], params[1], params[2], params[3], params[4], case.stride, case.pad,
+                                      case.dil, case.cpg, case.G, "exact", False)
+    got = torch.autograd.grad(y, params, dy)
+    conv = torch.nn.functional.conv3d if case.ndim == 3 else torch.nn.functional.conv2d
+    fn = dcn.ConvOffset3dFunction if case.ndim == 3 else dcn.ConvOffset2dFunction
+    ref_p = [t.clone().requires_grad_(True) for t in (x, w_off, b_off, w, b)]
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        o = conv(ref_p[0], ref_p[1], ref_p[2], stride=case.stride, padding=case.pad)
+        y_ref = fn.apply(ref_p[0], o, ref_p[3], ref_p[4], case.stride, case.pad, case.dil, case.cpg, case.G, "exact", False)
+        want = torch.autograd.grad(y_ref, ref_p, dy)
+    assert cases.rel_err(y.detach().cpu().numpy(), y_ref.detach().cpu().numpy()) <= 1e-4
+    for name, a, r in zip(("dx", "doffset_weight", "doffset_bias", "dweight", "dbias"), got, want):
+        assert cases.rel_err(a.cpu().numpy(), r.cpu().numpy()) <= 2e-4, (name, case)
