@@ -502,10 +502,16 @@ small_backward_kernel(const Geom g, const float* __restrict__ x, const float* __
     }
 }
 
-// fp32 deformable problems of at most 2^24 multiply-adds per pass whose group weights fit the shared memory.
+// fp32 deformable problems of at most 2^25 multiply-adds per pass whose group weights fit the shared memory.
 inline bool small_supported(const Geom& g, int dtype, int ndim, int deform) {
     if (dtype != 0 || !deform) return false;
-    if ((double)g.P * g.Kg * g.Og * g.G > 16777216.0) return false;
+    // multiply-adds per pass up to which these kernels are taken (DCN_SMALL_LOG2 overrides the exponent)
+    static const double limit = [] {
+        const char* e = getenv("DCN_SMALL_LOG2");
+        const int lg = e != nullptr ? atoi(e) : 25;     // measured crossover with the tiled kernels: 2^25 .. 2^25.2
+        return (double)(1ull << (lg < 0 ? 0 : (lg > 40 ? 40 : lg)));
+    }();
+    if ((double)g.P * g.Kg * g.Og * g.G > limit) return false;
     const SmallDims d = small_dims(g, ndim);
     return d.smem_bwd <= 96 * 1024 && d.smem_fwd <= 96 * 1024;
 }
