@@ -256,8 +256,9 @@ BwdWeightWorkspace bwd_weight_workspace(const Geom& g) {
 }
 
 struct BwdDataWorkspace {
-    size_t xcl_off, dpk_off, wpk_off, scale_off, wt_off, dxcl_off, dxcl_bytes, dwpk_off, total;   // dwpk: fused backward only
+    size_t xcl_off, dpk_off, wpk_off, scale_off, wt_off, dxcl_off, dxcl_bytes, dwpk_off, gath_off, total;   // dwpk: fused backward only; gath: forward workspace of the transposed convolution
 };
+size_t gather_dgrad_bytes(const Geom& g);      // 0 unless the problem can take the gather form (any ndim)
 BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     const DgDims d = dg_dims(g);
     BwdDataWorkspace w;
@@ -273,8 +274,90 @@ BwdDataWorkspace bwd_data_workspace(const Geom& g) {
     // the shared-memory-accumulating kernel has no channels-last dX scratch; its sampling-point entries live there
     if (g.Cg % 8 == 0 && b2_points_bytes(g) > w.dxcl_bytes) w.dxcl_bytes = align_up(b2_points_bytes(g), 256);
     w.dwpk_off = w.dxcl_off + w.dxcl_bytes;
-    w.total = w.dwpk_off + align_up(dwpk_bytes(g), 256);
+    w.gath_off = w.dwpk_off + align_up(dwpk_bytes(g), 256);
+    w.total = w.gath_off + gather_dgrad_bytes(g);
     return w;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Plain convolution, stride 1: the input gradient is itself a plain convolution of dy (taps mirrored, weights
+// transposed within each group, padding dil*(k-1) - pad), so it runs on the FORWARD kernel as a gather -- every
+// dX element written once, no reductions -- instead of the scatter the deformable operator needs.
+// gt: that convolution's geometry (C and O swapped, input and output sizes swapped).
+// ---------------------------------------------------------------------------------------------------
+bool transposed_geom(const Geom& g, int ndim, Geom& gt) {
+    gt = g;
+    gt.C = g.O; gt.O = g.C;
+    gt.cpg = gt.C; gt.dg = 1; gt.oob = 0;
+    gt.iv = g.ov; gt.ov = g.iv;
+    for (int d = 0; d < 3; ++d) {
+        if (g.stride[d] != 1) return false;
+        gt.in[d] = g.out[d]; gt.out[d] = g.in[d];
+        gt.pad[d] = g.dil[d] * (g.k[d] - 1) - g.pad[d];
+        if (gt.pad[d] < 0) return false;
+        if (gt.in[d] + 2 * gt.pad[d] - g.dil[d] * (g.k[d] - 1) != gt.out[d]) return false;
+    }
+    gt.Cg = g.Og; gt.Og = g.Cg; gt.Kg = gt.Cg * gt.kv;
+    gt.P = (long long)gt.N * gt.ov;
+    gt.d_ov.init(gt.ov); gt.d_ow.init(gt.out[2]); gt.d_oh.init(gt.out[1]);
+    gt.d_Cg.init(gt.Cg); gt.d_cpg.init(gt.cpg);
+    (void)ndim;
+    return gt.Cg % 8 == 0 && gt.N <= 65535;
+}
+
+bool use_gather_dgrad(const Geom& g, int ndim, int deform, Geom& gt) {
+    static const bool off = [] { const char* e = getenv("DCN_GATHER_DGRAD"); return e != nullptr && e[0] == '0'; }();
+    return !off && !deform && transposed_geom(g, ndim, gt);
+}
+
+// Wt'[c][tap' * Og + ol] = W[j*Og + ol][cl][kv - 1 - tap'] (c = j*Cg + cl) as bf16: the k-major weights of the
+// transposed convolution, in the layout pack_weight_fwd reads.
+__global__ void __launch_bounds__(256)
+weight_flip_to_kmajor_bf16(const Geom g, const float* __restrict__ w, __nv_bfloat16* __restrict__ wt) {
+    const long long total = (long long)g.C * g.kv * g.Og;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int ol = (int)(i % g.Og);
+        const long long r = i / g.Og;
+        const int tap = (int)(r % g.kv);
+        const int c = (int)(r / g.kv);
+        const int j = c / g.Cg, cl = c - j * g.Cg;
+        wt[i] = __float2bfloat16_rn(__ldg(w + ((size_t)(j * g.Og + ol) * g.Cg + cl) * g.kv + (g.kv - 1 - tap)));
+    }
+}
+
+size_t gather_dgrad_bytes(const Geom& g) {
+    Geom gt;
+    if (g.dg != 1 || g.cpg != g.C) return 0;                     // deformable problems never take it
+    if (!transposed_geom(g, 3, gt)) return 0;
+    return align_up(fwd_workspace(gt).total, 256);
+}
+
+// dX of a plain stride-1 convolution through the forward kernel.  add: dX already holds a partial result (the
+// layer's deformable part, or the accumulating entry point): the tiles are added to it with reductions.
+// dx_cl: dX is stored channels-last (it may differ from the layout of dy: the layer's dOffset is always channel-first).
+int run_gather_dgrad(const Geom& g, const Geom& gt, int ndim, const float* w, const float* dy, float* dx, bool add,
+                     bool dx_cl, void* ws, cudaStream_t st) {
+    const FwdWorkspace l = fwd_workspace(gt);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    __nv_bfloat16* dycl = reinterpret_cast<__nv_bfloat16*>(base + l.xcl_off);
+    uint8_t* wpk = base + l.wpk_off;
+    __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(base + l.wt_off);
+    const TcDims d = tc_dims(gt);
+    int r = launch_channels_last(gt, dy, dycl, st);              // gt.cl == g.cl: dy has the layout of y
+    if (r != 0) return r;
+    {
+        const long long total = (long long)g.C * g.kv * g.Og;
+        const int blocks = (int)((total + 255) / 256 < 8ll * sm_count() ? (total + 255) / 256 : 8ll * sm_count());
+        weight_flip_to_kmajor_bf16<<<blocks, 256, 0, st>>>(g, w, wt);
+        if (cudaGetLastError() != cudaSuccess) return -5;
+    }
+    pack_weight_fwd<<<gt.G * d.MT * d.KC, 256, 0, st>>>(gt, wt, wpk, d.MT, d.KC);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    Geom gk = gt;
+    gk.cl = dx_cl ? 1 : 0;
+    // add: the tiles leave through reductions into the dX that is already there
+    return ndim == 2 ? launch_tc_forward<2, false>(gk, dycl, nullptr, wpk, nullptr, dx, st, add)
+                     : launch_tc_forward<3, false>(gk, dycl, nullptr, wpk, nullptr, dx, st, add);
 }
 
 // The shared-memory-accumulating backward-data kernel is taken whenever it fits (DCN_BWD2D=0 forces the
@@ -329,7 +412,11 @@ size_t tc_workspace_bytes(const Geom& g, int ndim, int pass) {
 // Kernels a pass enqueues when every gradient is wanted (memsets not counted).
 int tc_launch_count(const Geom& g, int ndim, int deform, int pass) {
     const bool b2 = use_bwd2d(g, ndim, deform);
+    Geom gt;
+    const bool gather = use_gather_dgrad(g, ndim, deform, gt);
     if (pass == 0) return 4;      // channels-last copy, weight reorder, weight tiles, implicit GEMM
+    if (gather && pass == 1) return 4;      // dy copy, mirrored weights, weight tiles, forward kernel on dy (adds into dX)
+    if (gather && pass == 3) return 8;      // the first four of those + input copy, dy pack, wgrad, dW unpack
     if (pass == 1) {
         if (b2) return 6;         // input copy, sampling points, dy pack, weight reorder, slab tiles, GEMM + scatter
         return g.cl ? 5 : 6;      // input copy, dy pack, weight reorder, weight tiles, GEMM + scatter, (dx transpose-add)
@@ -410,6 +497,11 @@ int tc_backward_data(const Geom& g, int ndim, int deform, const float* x, const 
         return run_bwd2d(g, xcl, off, w, dy, dpk, wpk, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off),
                          reinterpret_cast<unsigned int*>(base + l.scale_off),
                          reinterpret_cast<uint4*>(base + l.dxcl_off), dx, doff, true, st);
+    {
+        Geom gt;
+        if (dx != nullptr && use_gather_dgrad(g, ndim, deform, gt))          // plain, stride 1: a gather, added to dx
+            return run_gather_dgrad(g, gt, ndim, w, dy, dx, true, g.cl != 0, base + l.gath_off, st);
+    }
     r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
     if (r != 0) return r;
     r = launch_weight_to_kmajor(g, w, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off), nullptr, st);
@@ -494,7 +586,13 @@ int tc_backward(const Geom& g, int ndim, int deform, const float* x, const float
         r = launch_pack_dy(g, dy, dpk, d.MT, d.PC2, st);
         if (r != 0) return r;
     }
-    if (!b2 && (dx != nullptr || doff != nullptr)) {
+    Geom gt;
+    const bool gather = !b2 && dx != nullptr && use_gather_dgrad(g, ndim, deform, gt);
+    if (gather) {                                                          // plain, stride 1: dX as a gather
+        r = run_gather_dgrad(g, gt, ndim, w, dy, dx, false, g.cl != 0, base + l.gath_off, st);
+        if (r != 0) return r;
+    }
+    if (!b2 && !gather && (dx != nullptr || doff != nullptr)) {
         r = launch_weight_to_kmajor(g, w, reinterpret_cast<__nv_bfloat16*>(base + l.wt_off), nullptr, st);
         if (r != 0) return r;
         pack_weight_bwd<<<g.G * d.NB * d.OC, 256, 0, st>>>(g, reinterpret_cast<const __nv_bfloat16*>(base + l.wt_off), wpk,
@@ -573,6 +671,12 @@ static int plain_backward_into(const Geom& gq, int ndim, bool dx_channels_last, 
     const DgDims d = dg_dims(gq);
     int r = launch_pack_dy(gq, dyq, dpk, d.MT, d.PC2, st);
     if (r != 0) return r;
+    Geom gt;
+    if (dx != nullptr && use_gather_dgrad(gq, ndim, 0, gt)) {      // stride 1: a gather, added to the dX already there
+        r = run_gather_dgrad(gq, gt, ndim, w_off, dyq, dx, true, dx_channels_last, base + l.gath_off, st);
+        if (r != 0) return r;
+        dx = nullptr;                                              // done
+    }
     if (dx != nullptr) {
         __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(base + l.wt_off);
         r = launch_weight_to_kmajor(gq, w_off, wt, nullptr, st);

@@ -39,6 +39,7 @@ struct FwdCtl {            // lives behind the stages, the tables and the offset
 struct FwdSplit {
     long long T0, tile1, n_items;
     int KS0, cpk0, KS1, cpk1;
+    int acc;            // y already holds a partial result: every tile is added to it with reductions
 };
 struct FwdItem {
     long long tt;       // tile index ((j * MB + mb) * PT + pt)
@@ -54,7 +55,7 @@ __device__ __forceinline__ FwdItem fwd_item(const FwdSplit& sp, long long t, int
     it.tt = (tail ? sp.tile1 : 0) + r / KS;
     it.kc0 = it.ks * cpk;
     it.kc1 = (it.kc0 + cpk < KC) ? it.kc0 + cpk : KC;
-    it.atomic = KS > 1;
+    it.atomic = KS > 1 || sp.acc != 0;
     return it;
 }
 
@@ -510,9 +511,10 @@ inline int max_slots_per_chunk(const Geom& g, int cols_per_chunk) {
     return best;
 }
 
+// accumulate: add to what y holds (no zero fill; every tile leaves through reductions)
 template <int D, bool DEFORM>
 int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off, const uint8_t* wpk,
-                      const float* bias, float* y, cudaStream_t st) {
+                      const float* bias, float* y, cudaStream_t st, bool accumulate = false) {
     const TcDims d = tc_dims(g);
     const int max_slots = max_slots_per_chunk(g, 8);
     const size_t tab_one = (size_t)max_slots * 128 * sizeof(TabEntry<D, DEFORM>);
@@ -529,7 +531,10 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     for (const auto& c : pref) {
         if (need(c[0], c[1]) <= kSmemLimit) { stages = c[0]; n_tabs = c[1]; break; }
     }
-    if (stages == 0) return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
+    if (stages == 0) {
+        if (accumulate) return -5;                  // (the direct variant overwrites)
+        return launch_tc_forward_direct<D, DEFORM>(g, xcl, off, wpk, bias, y, st);   // table too large
+    }
     const int smem = (int)need(stages, n_tabs);
     constexpr int GW = 16;
     auto kern = tc_forward_kernel<D, DEFORM, GW>;
@@ -538,6 +543,7 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     const long long base_tiles = (long long)g.G * d.MB * d.PT;
     const int S = sm_count();
     FwdSplit sp;
+    sp.acc = accumulate ? 1 : 0;
     sp.KS0 = 1;
     if (base_tiles * 2 <= S) {
         sp.KS0 = (int)(S / base_tiles);
@@ -552,8 +558,8 @@ int launch_tc_forward(const Geom& g, const __nv_bfloat16* xcl, const float* off,
     sp.cpk1 = d.KC;
     sp.n_items = sp.T0;
     if (sp.KS0 > 1) {
-        if (cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
-    } else if (g.G * d.MB == 1 && base_tiles > S && base_tiles % S != 0) {
+        if (!accumulate && cudaMemsetAsync(y, 0, (size_t)g.N * g.O * g.ov * sizeof(float), st) != cudaSuccess) return -5;
+    } else if (!accumulate && g.G * d.MB == 1 && base_tiles > S && base_tiles % S != 0) {
         // Tail of an uneven grid: the R tiles left after the last full wave are split along K into as many pieces
         // as there are SMs to take them.  With one (group, channel block) the tile index is the position tile, so
         // the tail is the position range [P0, P) and only that part of y is zero-filled.

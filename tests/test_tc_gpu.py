@@ -68,6 +68,38 @@ def test_bf16_plain_conv3d():
     assert cases.rel_err(hw.cpu().numpy(), gw.cpu().numpy()) <= TOL_BF16
 
 
+@pytest.mark.parametrize("ndim,channels_last", [(2, False), (3, False), (3, True)])
+def test_bf16_plain_conv_stride1_input_gradient_as_gather(ndim, channels_last):
+    """Stride-1 plain convolution: the input gradient runs on the forward kernel as a convolution of dy with
+    mirrored taps and transposed weights (conv2d/lib/conv2d_cuda.cpp:184-191 + col2im in the reference).  Dilation,
+    groups, rectangular kernel and non-square padding; through the fused (overwriting) and the accumulating entry."""
+    import deform_conv3d_pytorch_op_b200 as dcn
+    g = torch.Generator().manual_seed(12)
+    size = (13, 11) if ndim == 2 else (5, 9, 8)
+    k = (3, 2) if ndim == 2 else (2, 3, 3)
+    pad = (2, 1) if ndim == 2 else (1, 2, 0)
+    dil = (2, 1) if ndim == 2 else (1, 2, 1)
+    x = torch.randn((2, 32) + size, generator=g).cuda()
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last_3d)
+    w = (torch.randn((48, 16) + k, generator=g) * 0.1).cuda()
+    conv = torch.nn.functional.conv3d if ndim == 3 else torch.nn.functional.conv2d
+    xr, wr = x.detach().clone().requires_grad_(True), w.clone().requires_grad_(True)
+    with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+        ref = conv(xr, wr, None, stride=1, padding=pad, dilation=dil, groups=2)
+        dy = torch.randn_like(ref)
+        gx, gw = torch.autograd.grad(ref, [xr, wr], dy)
+    op = dcn.Op(x, w, 1, pad, dil, 32, 2, deformable=False, std_size_rule=True, precision="bf16")
+    assert op.channels_last == channels_last
+    dx, _, dw, _ = op.backward(x, None, w, dy, True, False, True, False)
+    _check_status()
+    assert cases.rel_err(dx.cpu().numpy(), gx.cpu().numpy()) <= TOL_BF16
+    assert cases.rel_err(dw.cpu().numpy(), gw.cpu().numpy()) <= TOL_BF16
+    dx2, _ = op.backward_data(x, None, w, dy)              # accumulates into a zeroed buffer
+    _check_status()
+    assert cases.rel_err(dx2.cpu().numpy(), dx.cpu().numpy()) <= 1e-6
+
+
 def test_bf16_is_deterministic_in_forward():
     case = cases.TC_CASES[0]
     tensors = cases.make_inputs(case)
