@@ -738,6 +738,38 @@ def main():
         e2e = {"value": wl.flops() * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
+    # ---- the same workload as a LAYER (offset-producing convolution + deformable convolution in one library call,
+    # the caller pattern of deform3d/test_model.py:18-30): times only, outside the timed region of `value`.  A failure
+    # here must not cost the bench line, so it is reported as null.
+    layer_obj = None
+    if rank == 0 and not args.no_model:
+        try:
+            g = torch.Generator(device="cpu").manual_seed(1)
+            ow = (torch.randn(op.offset_weight_shape(), generator=g) * 0.02).to(dev)
+            ob = torch.zeros(op.offset_channels, device=dev)
+            yl, offl, wsl = op.layer_forward(x, ow, ob, w, None, keep_workspace=True)
+
+            def _t(fn, reps=10):
+                for _ in range(2):
+                    fn()
+                torch.cuda.synchronize(dev)
+                a, b = ev(), ev()
+                a.record()
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize(dev)
+                return a.elapsed_time(b) / reps
+            layer_obj = {
+                "forward_ms": _t(lambda: op.layer_forward(x, ow, ob, w, None)),
+                "backward_ms": _t(lambda: op.layer_backward(x, offl, ow, w, dy, True, True, True, True, False, wsl)),
+                "launches": [int(_lib.lib().dcn_layer_launch_count(ctypes.byref(op.p), ps)) for ps in (0, 3)],
+                "offset_channels": int(op.offset_channels), "offset_weight_std": 0.02,
+            }
+            del yl, offl, wsl, ow, ob
+        except Exception as exc:                                  # pragma: no cover
+            layer_obj = {"error": str(exc)[:200]}
+
     # ---- the model-level workload (config 5) of the same metric, on the same ranks, as the `model` object ----
     model_obj = None
     if not args.no_model:
@@ -795,7 +827,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if prec == "bf16" else "f32", "data": "synthetic",
             "config": our_config(wl, prec, world, flush, working_set),
-            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "model": model_obj,
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "model": model_obj, "layer": layer_obj,
             "gpu_launches": launches_per_step * args.steps,
         }
         print(json.dumps(line), flush=True)
